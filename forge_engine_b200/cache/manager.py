@@ -23,11 +23,18 @@ from .pages import BlockTable, PagePool, StateSlots
 
 @dataclass(frozen=True)
 class PagedKVSpec:
-    """Keys and values of ``num_kv_heads`` heads of ``head_dim``; ``window`` None keeps all."""
+    """Keys and values of ``num_kv_heads`` heads of ``head_dim``; ``window`` None keeps all.
+    ``v_head_dim``: size of a value head where it differs (None: ``head_dim``; 0: the run
+    keeps one vector per token and head, no second one - a latent that is key and value)."""
 
     num_kv_heads: int
     head_dim: int
     window: int | None = None
+    v_head_dim: int | None = None
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
 
 
 @dataclass(frozen=True)
@@ -54,7 +61,9 @@ class LayerGroup:
     spec: PagedKVSpec
     units: list  # run indices that own a cache in this group
     pool: PagePool
-    storage: object = None  # [units, 2, pages, kv_heads, page_size, head_dim]
+    # [units, 2, pages, kv_heads, page_size, head_dim]; where values have another size than
+    # keys, one flat tensor: per unit all key pages, then all value pages
+    storage: object = None
 
     def unit_slot(self, run: int) -> int:
         return self.units.index(run)
@@ -144,6 +153,9 @@ class CacheManager:
             # one page more than the pool leases: ``null_page`` takes the keys of filler
             # entries of fixed-size (graph-replayed) batches and is never read back
             shape = (len(group.units), 2, self.num_pages + 1, spec.num_kv_heads, self.page_size, spec.head_dim)
+            if spec.value_dim != spec.head_dim:
+                rows = (self.num_pages + 1) * spec.num_kv_heads * self.page_size
+                shape = (len(group.units) * rows * (spec.head_dim + spec.value_dim),)
             numel = 1
             for extent in shape:
                 numel *= extent
@@ -168,7 +180,7 @@ class CacheManager:
 
         size = torch.empty((), dtype=self.dtype).element_size() if self.dtype is not None else 2
         return sum(
-            2 * len(g.units) * g.spec.num_kv_heads * g.spec.head_dim * size for g in self.groups
+            len(g.units) * g.spec.num_kv_heads * (g.spec.head_dim + g.spec.value_dim) * size for g in self.groups
         )
 
     def group_of_run(self, run: int) -> int | None:
@@ -176,10 +188,21 @@ class CacheManager:
         return None if entry is None else entry[0]
 
     def kv_of_run(self, run: int) -> tuple:
-        """(k_cache, v_cache) tensors [pages, kv_heads, page_size, head_dim] of a run."""
+        """(k_cache, v_cache) tensors [pages, kv_heads, page_size, head_dim] of a run (the
+        values with their own last extent; None for a run that keeps no second vector)."""
         group_index, unit = self._run_group[run]
-        storage = self.groups[group_index].storage
-        return storage[unit, 0], storage[unit, 1]
+        group = self.groups[group_index]
+        storage, spec = group.storage, group.spec
+        if spec.value_dim == spec.head_dim:
+            return storage[unit, 0], storage[unit, 1]
+        lead = (self.num_pages + 1, spec.num_kv_heads, self.page_size)
+        rows = lead[0] * lead[1] * lead[2]
+        begin = unit * rows * (spec.head_dim + spec.value_dim)
+        keys = storage[begin : begin + rows * spec.head_dim].view(*lead, spec.head_dim)
+        if spec.value_dim == 0:
+            return keys, None
+        begin += rows * spec.head_dim
+        return keys, storage[begin : begin + rows * spec.value_dim].view(*lead, spec.value_dim)
 
     def view(self, run: int):
         """The CacheView a mixer gets for run ``run``."""

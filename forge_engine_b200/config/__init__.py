@@ -12,16 +12,25 @@ from .registry import (
 from .specs import (
     AttentionSpec,
     GatedMLPSpec,
+    LatentAttentionSpec,
+    LayerNormSpec,
     LayerSpec,
+    LinearRecurrenceSpec,
     ModelSpec,
     NoPositionSpec,
     NormSpec,
     RotarySpec,
     RunSpec,
+    StreamMixSpec,
 )
+from .zofadra import ZofadraConfig
 
 register_architecture(
     Architecture("Qwen3ForCausalLM", Qwen3Config.from_dict, Qwen3Config.to_model_spec),
+    replace=True,
+)
+register_architecture(
+    Architecture("Zofadra", ZofadraConfig.from_dict, ZofadraConfig.to_model_spec),
     replace=True,
 )
 
@@ -30,7 +39,10 @@ __all__ = [
     "AttentionSpec",
     "EngineConfig",
     "GatedMLPSpec",
+    "LatentAttentionSpec",
+    "LayerNormSpec",
     "LayerSpec",
+    "LinearRecurrenceSpec",
     "ModelSpec",
     "NoPositionSpec",
     "NormSpec",
@@ -38,6 +50,8 @@ __all__ = [
     "RotarySpec",
     "RunSpec",
     "SchedulerConfig",
+    "StreamMixSpec",
+    "ZofadraConfig",
     "architecture_of",
     "known_architectures",
     "read_model_config",

@@ -1,7 +1,8 @@
 """One registry from an architecture's name to its configuration and model spec.
 
 Upstream has no registry (one pinned checkpoint; docs/architecture.md:67-70 says so);
-this is the single place where ``config.json``'s ``architectures[0]`` is looked up.
+this is the single place where ``config.json``'s ``architectures[0]`` (or its
+``architecture``, a single name) is looked up.
 """
 
 from __future__ import annotations
@@ -65,12 +66,13 @@ def known_architectures() -> tuple:
 
 
 def architecture_of(raw: dict) -> Architecture:
-    names = raw.get("architectures") or []
+    names = raw.get("architectures") or raw.get("architecture") or []
     if isinstance(names, str):
         names = [names]
     if not names:
         raise ConfigError(
-            "config.json has no 'architectures' entry; known: " + ", ".join(known_architectures())
+            "config.json has neither an 'architectures' nor an 'architecture' entry; known: "
+            + ", ".join(known_architectures())
         )
     name = names[0]
     if name not in _ARCHITECTURES:

@@ -12,6 +12,18 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 
 
+def local_name(spec, canonical: str) -> str:
+    """The name a part's tensor has in its checkpoint, relative to the part's prefix.
+    ``spec.rename`` is a tuple of (canonical, stored) pairs; a stored name "" means that
+    the tensor is called by the prefix alone."""
+    return dict(getattr(spec, "rename", ()) or ()).get(canonical, canonical)
+
+
+def join_name(prefix: str, local: str) -> str:
+    """Checkpoint name of a part's tensor: ``prefix.local``, or ``prefix`` for local ""."""
+    return f"{prefix}.{local}" if local else prefix
+
+
 @dataclass(frozen=True)
 class NormSpec:
     """RMS normalisation over the last ``size`` elements."""
@@ -19,6 +31,18 @@ class NormSpec:
     size: int
     eps: float
     kind: str = "rmsnorm"
+    rename: tuple = ()
+
+
+@dataclass(frozen=True)
+class LayerNormSpec:
+    """(x - mean) / sqrt(variance + eps) * weight over the last ``size`` elements, the
+    variance being the mean of the squared deviations; no bias."""
+
+    size: int
+    eps: float
+    kind: str = "layernorm"
+    rename: tuple = ()
 
 
 @dataclass(frozen=True)
@@ -33,6 +57,8 @@ class RotarySpec:
     theta: float
     rotary_dim: int
     kind: str = "rope"
+    # False: element j is paired with j + rotary_dim/2; True: element 2j with 2j + 1.
+    interleaved: bool = False
 
 
 @dataclass(frozen=True)
@@ -61,6 +87,59 @@ class AttentionSpec:
     position: object
     window: int | None = None
     kind: str = "gqa_attention"
+    # Size of a value head where it differs from ``head_dim`` (None: the same).
+    v_head_dim: int | None = None
+    # "head": q and k are normalised head by head with weights of ``head_dim`` (when
+    # ``qk_norm``); "whole": over all heads of the projection at once, with weights of the
+    # projection's size.
+    qk_norm_scope: str = "head"
+    # None, or the base b of a bias on the distance: head h of H takes
+    # b^(-(h + 1) / H) * (i - j) off the score of query i and key j (b = 2^8 gives the
+    # slopes 2^(-8 (h + 1) / H)).
+    distance_bias_base: float | None = None
+    rename: tuple = ()
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Causal attention whose keys and values are expanded from one cached latent.
+
+    Per head ``head_dim`` query/key elements that are not rotated and ``rot_dim`` that are;
+    the rotated key part is one vector shared by all heads.  Cached per token: the
+    normalised latent (``kv_rank``) and the rotated key part (``rot_dim``).  ``kv_from``
+    None: the layer projects and caches its own latent; otherwise it reads the cache of
+    the layer of that index.  ``position`` is a RotarySpec for the ``rot_dim`` part."""
+
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    rot_dim: int
+    v_head_dim: int
+    q_rank: int
+    kv_rank: int
+    norm_eps: float
+    scale: float
+    position: object
+    kv_from: int | None = None
+    kind: str = "latent_attention"
+    rename: tuple = ()
+
+
+@dataclass(frozen=True)
+class LinearRecurrenceSpec:
+    """Linear attention with a fixed decay per head ("lightning" attention):
+    S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t with q, k, v = act(W x); the heads'
+    outputs are RMS-normalised together, gated by sigmoid(W_g x) and projected."""
+
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    v_head_dim: int
+    decay: tuple
+    norm_eps: float
+    activation: str = "silu"
+    kind: str = "linear_recurrence"
+    rename: tuple = ()
 
 
 @dataclass(frozen=True)
@@ -69,8 +148,9 @@ class GatedMLPSpec:
 
     hidden_size: int
     intermediate_size: int
-    activation: str = "silu"
+    activation: str = "silu"      # "silu" or "gelu_tanh"
     kind: str = "gated_mlp"
+    rename: tuple = ()
 
 
 @dataclass(frozen=True)
@@ -88,6 +168,21 @@ class LayerSpec:
     ffn: object
     names: dict = field(default_factory=dict, hash=False, compare=False)
     arrangement: str = "pre_norm"
+    # What an arrangement other than "pre_norm" needs to know (a frozen dataclass of its own).
+    options: object = None
+
+
+@dataclass(frozen=True)
+class StreamMixSpec:
+    """Options of the "stream_mix" arrangement: ``streams`` copies of the residual stream
+    that every sublayer reads as a weighted sum and writes back through a mixing matrix
+    (``learned`` True: weights ``in`` [streams], ``out`` [streams], ``mix`` [streams, streams]
+    per sublayer in the checkpoint; False: one stream and the plain residual sum), the
+    sublayer's output scaled by ``update_scale``."""
+
+    streams: int = 1
+    learned: bool = False
+    update_scale: float = 1.0
 
 
 @dataclass(frozen=True)
@@ -118,3 +213,5 @@ class ModelSpec:
     embed_name: str = "model.embed_tokens.weight"
     final_norm_name: str = "model.norm"
     head_name: str = "lm_head.weight"
+    embedding_scale: float = 1.0     # the embedding rows are multiplied by this
+    residual_streams: int = 1        # copies of the residual stream (see StreamMixSpec)

@@ -7,33 +7,39 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------------------
-// embedding: residual[n, :] = float(table[ids[n], :])
+// embedding: residual[n, c, :] = float(table[ids[n], :]) * scale for each of `copies` streams
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
-                                 float* __restrict__ out, int hidden, int vocab, int* status) {
+                                 float* __restrict__ out, int hidden, int vocab, float scale, int copies,
+                                 int* status) {
   pdl_trigger();
   pdl_wait();
   const int row = blockIdx.x;
   const int id = ids[row];
-  float* dst = out + (size_t)row * hidden;
+  float* dst = out + (size_t)row * copies * hidden;
   if (id < 0 || id >= vocab) {
     if (threadIdx.x == 0) atomicOr(status, FE_STATUS_BAD_TOKEN);
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = 0.f;
+    for (int i = threadIdx.x; i < copies * hidden; i += blockDim.x) dst[i] = 0.f;
     return;
   }
   const T* src = table + (size_t)id * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_float(src[i]);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float v = scale == 1.f ? to_float(src[i]) : to_float(src[i]) * scale;
+    for (int c = 0; c < copies; ++c) dst[(size_t)c * hidden + i] = v;
+  }
 }
 
 FE_EXPORT int fe_embedding(const int* ids, const void* table, int table_dtype, float* out,
-                           int n, int hidden, int vocab, int* status, cudaStream_t stream) {
+                           int n, int hidden, int vocab, float scale, int copies, int* status,
+                           cudaStream_t stream) {
   if (n <= 0) return 0;
+  if (copies < 1) return FE_ERR_BAD_SHAPE;
   const int threads = hidden >= 1024 ? 256 : 128;
   if (table_dtype == FE_DTYPE_F32)
-    return fe_launch_dependent(embedding_kernel<float>, dim3(n), dim3(threads), 0, stream, ids, (const float*)table, out, hidden, vocab, status);
+    return fe_launch_dependent(embedding_kernel<float>, dim3(n), dim3(threads), 0, stream, ids, (const float*)table, out, hidden, vocab, scale, copies, status);
   else if (table_dtype == FE_DTYPE_BF16)
-    return fe_launch_dependent(embedding_kernel<bf16>, dim3(n), dim3(threads), 0, stream, ids, (const bf16*)table, out, hidden, vocab, status);
+    return fe_launch_dependent(embedding_kernel<bf16>, dim3(n), dim3(threads), 0, stream, ids, (const bf16*)table, out, hidden, vocab, scale, copies, status);
   else
     return FE_ERR_BAD_DTYPE;
   return fe_last_error();

@@ -14,7 +14,12 @@
 template <typename TX, typename TW, typename TY>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TX* __restrict__ x, const TW* __restrict__ w, const float* __restrict__ bias,
-                 TY* __restrict__ y, int n, int o, int k, int accumulate) {
+                 TY* __restrict__ y, int n, int o, int k, int accumulate, long long ldx, long long ldy,
+                 long long batch_x, long long batch_w, long long batch_y) {
+  // blockIdx.z: one product of a batch (a head); rows of x and y may be wider than k and o
+  x += (size_t)blockIdx.z * batch_x;
+  w += (size_t)blockIdx.z * batch_w;
+  y += (size_t)blockIdx.z * batch_y;
   __shared__ float xs[GS_BK][GS_BM + 4];
   __shared__ float ws[GS_BK][GS_BN + 4];
   const int tid = threadIdx.x;
@@ -32,7 +37,7 @@ gemm_simt_kernel(const TX* __restrict__ x, const TW* __restrict__ w, const float
     for (int e = 0; e < 4; ++e) {
       const int kk = k0 + lk + e;
       const int xr = row0 + lr, wr = col0 + lr;
-      xs[lk + e][lr] = (xr < n && kk < k) ? to_float(x[(size_t)xr * k + kk]) : 0.f;
+      xs[lk + e][lr] = (xr < n && kk < k) ? to_float(x[(size_t)xr * ldx + kk]) : 0.f;
       ws[lk + e][lr] = (wr < o && kk < k) ? to_float(w[(size_t)wr * k + kk]) : 0.f;
     }
     __syncthreads();
@@ -60,7 +65,7 @@ gemm_simt_kernel(const TX* __restrict__ x, const TW* __restrict__ w, const float
       if (c >= o) continue;
       float v = acc[i][j];
       if (bias) v += bias[c];
-      TY* dst = y + (size_t)r * o + c;
+      TY* dst = y + (size_t)r * ldy + c;
       if (accumulate) v += to_float(*dst);
       *dst = from_float<TY>(v);
     }
@@ -69,11 +74,13 @@ gemm_simt_kernel(const TX* __restrict__ x, const TW* __restrict__ w, const float
 
 template <typename TX, typename TW, typename TY>
 static int launch_simt(const void* x, const void* w, const float* bias, void* y, int n, int o, int k,
-                       int accumulate, cudaStream_t stream) {
-  dim3 grid((o + GS_BN - 1) / GS_BN, (n + GS_BM - 1) / GS_BM);
-  if (grid.y > 65535) return FE_ERR_TOO_LARGE;
+                       int accumulate, cudaStream_t stream, int batch = 1, long long ldx = 0, long long ldy = 0,
+                       long long batch_x = 0, long long batch_w = 0, long long batch_y = 0) {
+  dim3 grid((o + GS_BN - 1) / GS_BN, (n + GS_BM - 1) / GS_BM, batch);
+  if (grid.y > 65535 || batch > 65535) return FE_ERR_TOO_LARGE;
   gemm_simt_kernel<TX, TW, TY><<<grid, 256, 0, stream>>>((const TX*)x, (const TW*)w, bias, (TY*)y, n, o,
-                                                        k, accumulate);
+                                                        k, accumulate, ldx ? ldx : k, ldy ? ldy : o, batch_x,
+                                                        batch_w, batch_y);
   return fe_last_error();
 }
 
@@ -93,5 +100,30 @@ FE_EXPORT int fe_gemm_simt(const void* x, int x_dtype, const void* w, int w_dtyp
     case 6: return launch_simt<bf16, bf16, float>(x, w, bias, y, n, o, k, accumulate, stream);
     case 7: return launch_simt<bf16, bf16, bf16>(x, w, bias, y, n, o, k, accumulate, stream);
   }
+  return FE_ERR_BAD_DTYPE;
+}
+
+// `batch` products at once (one per head): product b reads x + b * batch_x (rows ldx apart),
+// the [o, k] matrix w + b * batch_w, and writes y + b * batch_y (rows ldy apart).  All strides
+// in elements.
+FE_EXPORT int fe_gemm_simt_batched(const void* x, int x_dtype, const void* w, int w_dtype, void* y, int y_dtype,
+                                   int n, int o, int k, int batch, long long ldx, long long ldy, long long batch_x,
+                                   long long batch_w, long long batch_y, cudaStream_t stream) {
+  if (n <= 0 || o <= 0 || batch <= 0) return 0;
+  if (k <= 0 || ldx < k || ldy < o) return FE_ERR_BAD_SHAPE;
+  const int code = x_dtype * 4 + w_dtype * 2 + y_dtype;
+#define BATCHED(TX, TW, TY) \
+  return launch_simt<TX, TW, TY>(x, w, nullptr, y, n, o, k, 0, stream, batch, ldx, ldy, batch_x, batch_w, batch_y)
+  switch (code) {
+    case 0: BATCHED(float, float, float);
+    case 1: BATCHED(float, float, bf16);
+    case 2: BATCHED(float, bf16, float);
+    case 3: BATCHED(float, bf16, bf16);
+    case 4: BATCHED(bf16, float, float);
+    case 5: BATCHED(bf16, float, bf16);
+    case 6: BATCHED(bf16, bf16, float);
+    case 7: BATCHED(bf16, bf16, bf16);
+  }
+#undef BATCHED
   return FE_ERR_BAD_DTYPE;
 }

@@ -1,0 +1,192 @@
+// Residual streams, their norms, and small token-wise kernels of layers built on them.
+//
+// stream_mix_norm: the residual stream exists in S copies x_1..x_S per token (S = 1: the
+// usual single stream).  One launch does, per token and all in 32-bit,
+//   x'_t = sum_s mix[s, t] x_s + c * out[t] * y          (y: the last sublayer's output)
+//   u    = sum_t in[t] x'_t
+//   z    = norm(u) * w                                   (RMS or layer norm, or none)
+// with every piece optional: no y (nothing to add), no mix (identity), no out / in (ones).
+// It is the fused "add the update, then normalise for the next sublayer" of a pre-norm
+// block, generalised to several streams and to a layer norm.
+//
+// act_mul: act(gate) * up for a row [gate | up]; gated_rmsnorm: rms(x) * w * sigmoid(g).
+#include "common.cuh"
+
+#define FE_MAX_STREAMS 8
+#define FE_NORM_NONE 0
+#define FE_NORM_RMS 1
+#define FE_NORM_LAYER 2
+
+template <typename TU, typename TO>
+__global__ void __launch_bounds__(256)
+stream_mix_norm_kernel(float* __restrict__ streams, int S, const TU* __restrict__ update, float update_scale,
+                       const float* __restrict__ mix, const float* __restrict__ out_coef,
+                       const float* __restrict__ in_coef, int norm_kind, const float* __restrict__ weight,
+                       float eps, TO* __restrict__ out, const int* __restrict__ row_map, int W,
+                       int write_streams) {
+  extern __shared__ float u_row[];          // [W]
+  __shared__ float scratch[33];
+  __shared__ float c_mix[FE_MAX_STREAMS * FE_MAX_STREAMS], c_out[FE_MAX_STREAMS], c_in[FE_MAX_STREAMS];
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const int src = row_map ? row_map[r] : r;
+  if (threadIdx.x < S * S) c_mix[threadIdx.x] = mix ? mix[threadIdx.x] : ((threadIdx.x / S) == (threadIdx.x % S) ? 1.f : 0.f);
+  if (threadIdx.x < S) {
+    c_out[threadIdx.x] = (out_coef ? out_coef[threadIdx.x] : 1.f) * update_scale;
+    c_in[threadIdx.x] = in_coef ? in_coef[threadIdx.x] : 1.f;
+  }
+  __syncthreads();
+  float* base = streams + (size_t)src * S * W;
+  const TU* upd = update ? update + (size_t)src * W : nullptr;
+  float total = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    float x[FE_MAX_STREAMS];
+#pragma unroll
+    for (int s = 0; s < FE_MAX_STREAMS; ++s) x[s] = s < S ? base[(size_t)s * W + i] : 0.f;
+    float u = 0.f;
+    if (upd) {
+      const float y = to_float(upd[i]);
+#pragma unroll
+      for (int t = 0; t < FE_MAX_STREAMS; ++t) {
+        if (t < S) {
+          float v = 0.f;
+#pragma unroll
+          for (int s = 0; s < FE_MAX_STREAMS; ++s)
+            if (s < S) v = fmaf(c_mix[s * S + t], x[s], v);
+          v = fmaf(c_out[t], y, v);
+          if (write_streams) base[(size_t)t * W + i] = v;
+          u = fmaf(c_in[t], v, u);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int t = 0; t < FE_MAX_STREAMS; ++t)
+        if (t < S) u = fmaf(c_in[t], x[t], u);
+    }
+    u_row[i] = u;
+    total += norm_kind == FE_NORM_RMS ? u * u : u;
+  }
+  if (out == nullptr || norm_kind == FE_NORM_NONE) {
+    if (out != nullptr)
+      for (int i = threadIdx.x; i < W; i += blockDim.x) out[(size_t)r * W + i] = from_float<TO>(u_row[i]);
+    return;
+  }
+  total = block_sum(total, scratch);
+  float mean = 0.f, inv;
+  if (norm_kind == FE_NORM_RMS) {
+    inv = 1.f / sqrtf(total / (float)W + eps);
+  } else {
+    mean = total / (float)W;
+    float dev = 0.f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+      const float d = u_row[i] - mean;
+      dev = fmaf(d, d, dev);
+    }
+    dev = block_sum(dev, scratch);
+    inv = 1.f / sqrtf(dev / (float)W + eps);
+  }
+  TO* dst = out + (size_t)r * W;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) dst[i] = from_float<TO>((u_row[i] - mean) * inv * weight[i]);
+}
+
+FE_EXPORT int fe_stream_mix_norm(float* streams, int n_streams, const void* update, int update_dtype,
+                                 float update_scale, const float* mix, const float* out_coef, const float* in_coef,
+                                 int norm_kind, const float* weight, float eps, void* out, int out_dtype,
+                                 const int* row_map, int rows, int width, int write_streams, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (n_streams < 1 || n_streams > FE_MAX_STREAMS || width < 1) return FE_ERR_BAD_SHAPE;
+  if (norm_kind != FE_NORM_NONE && out != nullptr && weight == nullptr) return FE_ERR_BAD_SHAPE;
+  const size_t smem = sizeof(float) * (size_t)width;
+  if (smem > 200 * 1024) return FE_ERR_TOO_LARGE;
+  const int threads = width >= 2048 ? 256 : 128;
+  int rc = 0;
+#define LAUNCH(TU, TO)                                                                                          \
+  do {                                                                                                          \
+    if (smem > 48 * 1024)                                                                                       \
+      cudaFuncSetAttribute(stream_mix_norm_kernel<TU, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    rc = fe_launch_dependent(stream_mix_norm_kernel<TU, TO>, dim3(rows), dim3(threads), smem, stream, streams,  \
+                             n_streams, (const TU*)update, update_scale, mix, out_coef, in_coef, norm_kind,     \
+                             weight, eps, (TO*)out, row_map, width, write_streams);                             \
+  } while (0)
+  const int ud = update ? update_dtype : FE_DTYPE_F32;
+  if (ud == FE_DTYPE_F32 && out_dtype == FE_DTYPE_F32) LAUNCH(float, float);
+  else if (ud == FE_DTYPE_BF16 && out_dtype == FE_DTYPE_BF16) LAUNCH(bf16, bf16);
+  else if (ud == FE_DTYPE_F32 && out_dtype == FE_DTYPE_BF16) LAUNCH(float, bf16);
+  else if (ud == FE_DTYPE_BF16 && out_dtype == FE_DTYPE_F32) LAUNCH(bf16, float);
+  else return FE_ERR_BAD_DTYPE;
+#undef LAUNCH
+  return rc ? rc : fe_last_error();
+}
+
+// ---------------------------------------------------------------------------
+// out[n, i] = act(gate_up[n, i]) * gate_up[n, inter + i];  act 0: SiLU, 1: the tanh form of GELU
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float act_apply(float z, int act) {
+  if (act == 0) return z / (1.f + expf(-z));
+  const float inner = 0.7978845608028654f * (z + 0.044715f * z * z * z);
+  return 0.5f * z * (1.f + tanhf(inner));
+}
+
+template <typename TI, typename TO>
+__global__ void act_mul_kernel(const TI* __restrict__ gate_up, TO* __restrict__ out, int inter, int act) {
+  pdl_trigger();
+  pdl_wait();
+  const int row = blockIdx.x;
+  const TI* g = gate_up + (size_t)row * 2 * inter;
+  TO* o = out + (size_t)row * inter;
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < inter; i += gridDim.y * blockDim.x)
+    o[i] = from_float<TO>(act_apply(to_float(g[i]), act) * to_float(g[inter + i]));
+}
+
+FE_EXPORT int fe_act_mul(const void* gate_up, int in_dtype, void* out, int out_dtype, int rows, int inter, int act,
+                         cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (act != 0 && act != 1) return FE_ERR_BAD_SHAPE;
+  const int threads = 256;
+  int chunks = (inter + threads - 1) / threads;
+  if (chunks > 64) chunks = 64;
+  dim3 grid(rows, chunks);
+  if (in_dtype == FE_DTYPE_F32 && out_dtype == FE_DTYPE_F32)
+    return fe_launch_dependent(act_mul_kernel<float, float>, grid, dim3(threads), 0, stream, (const float*)gate_up, (float*)out, inter, act);
+  if (in_dtype == FE_DTYPE_BF16 && out_dtype == FE_DTYPE_BF16)
+    return fe_launch_dependent(act_mul_kernel<bf16, bf16>, grid, dim3(threads), 0, stream, (const bf16*)gate_up, (bf16*)out, inter, act);
+  if (in_dtype == FE_DTYPE_F32 && out_dtype == FE_DTYPE_BF16)
+    return fe_launch_dependent(act_mul_kernel<float, bf16>, grid, dim3(threads), 0, stream, (const float*)gate_up, (bf16*)out, inter, act);
+  return FE_ERR_BAD_DTYPE;
+}
+
+// ---------------------------------------------------------------------------
+// out[n, :] = x[n, :] / sqrt(mean(x[n, :]^2) + eps) * weight * sigmoid(gate[n, :])
+// x is 32-bit [rows, size]; gate row n starts at gate + n * gate_stride.
+// ---------------------------------------------------------------------------
+template <typename TG, typename TO>
+__global__ void gated_rmsnorm_kernel(const float* __restrict__ x, const TG* __restrict__ gate, int gate_stride,
+                                     const float* __restrict__ weight, TO* __restrict__ out, int size, float eps) {
+  __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const float* xr = x + (size_t)r * size;
+  const TG* gr = gate + (size_t)r * gate_stride;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < size; i += blockDim.x) ss = fmaf(xr[i], xr[i], ss);
+  const float inv = 1.f / sqrtf(block_sum(ss, scratch) / (float)size + eps);
+  for (int i = threadIdx.x; i < size; i += blockDim.x) {
+    const float g = to_float(gr[i]);
+    out[(size_t)r * size + i] = from_float<TO>(xr[i] * inv * weight[i] * (1.f / (1.f + expf(-g))));
+  }
+}
+
+FE_EXPORT int fe_gated_rmsnorm(const float* x, const void* gate, int gate_dtype, int gate_stride, const float* weight,
+                               void* out, int out_dtype, int rows, int size, float eps, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  const int threads = size >= 1024 ? 256 : 128;
+  if (gate_dtype == FE_DTYPE_F32 && out_dtype == FE_DTYPE_F32)
+    return fe_launch_dependent(gated_rmsnorm_kernel<float, float>, dim3(rows), dim3(threads), 0, stream, x, (const float*)gate, gate_stride, weight, (float*)out, size, eps);
+  if (gate_dtype == FE_DTYPE_BF16 && out_dtype == FE_DTYPE_BF16)
+    return fe_launch_dependent(gated_rmsnorm_kernel<bf16, bf16>, dim3(rows), dim3(threads), 0, stream, x, (const bf16*)gate, gate_stride, weight, (bf16*)out, size, eps);
+  if (gate_dtype == FE_DTYPE_F32 && out_dtype == FE_DTYPE_BF16)
+    return fe_launch_dependent(gated_rmsnorm_kernel<float, bf16>, dim3(rows), dim3(threads), 0, stream, x, (const float*)gate, gate_stride, weight, (bf16*)out, size, eps);
+  return FE_ERR_BAD_DTYPE;
+}

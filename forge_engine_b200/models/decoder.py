@@ -1,7 +1,8 @@
 """A decoder-only language model assembled from a ModelSpec.
 
 Data flow of one step (src/forge_engine/qwen3.py:297-342, restated for a flat batch):
-embedding gather into the 32-bit residual stream, the runs of the schedule in order
+embedding gather (times the spec's scale) into the 32-bit residual stream - or into
+several copies of it, for arrangements that keep more than one -, the runs of the schedule in order
 (each a block with its cache view), final norm on the wanted rows only, and the output
 projection to 32-bit logits.  Which blocks exist, which run uses which block and which
 cache, is all data of the spec; this class has no sizes of its own.
@@ -13,7 +14,7 @@ from collections.abc import Mapping
 
 import torch
 
-from ..config.specs import ModelSpec
+from ..config.specs import ModelSpec, join_name
 from ..ops import native
 from ..parts.base import BuildContext, WeightInfo, arrangement_class, build_part, part_class
 from ..parts.linear import Linear
@@ -26,13 +27,13 @@ def expected_tensors(spec: ModelSpec) -> dict:
         spec.embed_name: WeightInfo((spec.vocab_size, spec.hidden_size)),
     }
     for local, info in part_class(spec.final_norm).weight_shapes(spec.final_norm).items():
-        out[f"{spec.final_norm_name}.{local}"] = info
+        out[join_name(spec.final_norm_name, local)] = info
     for layer in spec.layers:
         block = arrangement_class(layer.arrangement)
         for role, shapes in block.weight_shapes(layer).items():
             prefix = layer.names[role]
             for local, info in shapes.items():
-                out[f"{prefix}.{local}"] = info
+                out[join_name(prefix, local)] = info
     if not spec.tie_embeddings:
         out[spec.head_name] = WeightInfo((spec.vocab_size, spec.hidden_size))
     return out
@@ -49,7 +50,7 @@ class _Scoped(Mapping):
     def __getitem__(self, local: str):
         if local not in self._names:
             raise KeyError(local)
-        return self._weights[f"{self._prefix}.{local}"]
+        return self._weights[join_name(self._prefix, local)]
 
     def __iter__(self):
         return iter(self._names)
@@ -137,15 +138,23 @@ class DecoderModel:
         """Run ``batch`` through all runs; returns logits [wanted rows, vocab] in 32-bit."""
         n = batch.n_tokens
         batch.shared.clear()      # what parts share lives for one pass only (a batch may be run again)
-        h = torch.empty((n, self.spec.hidden_size), dtype=torch.float32, device=self.ctx.device)
+        streams = getattr(self.spec, "residual_streams", 1)
+        shape = (n, self.spec.hidden_size) if streams == 1 else (n, streams, self.spec.hidden_size)
+        h = torch.empty(shape, dtype=torch.float32, device=self.ctx.device)
         with self.ctx.section("embedding"):
-            native.embedding(batch.token_ids, self.embed, h, self.ctx.status)
+            native.embedding(batch.token_ids, self.embed, h, self.ctx.status,
+                             scale=getattr(self.spec, "embedding_scale", 1.0))
         pending = None
         for index, run in enumerate(self.spec.schedule):
             pending = self.blocks[run.layer].forward(h, pending, batch, cache.view(index))
         if batch.n_want == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.ctx.device)
+        # an arrangement whose pending update is more than a tensor folds it into the final norm itself
+        close = getattr(self.blocks[self.spec.schedule[-1].layer], "close", None)
         with self.ctx.section("final_norm"):
-            normed = self.final_norm.add_forward(h, pending, row_map=batch.want_rows)
+            if close is not None:
+                normed = close(h, pending, self.final_norm, batch.want_rows)
+            else:
+                normed = self.final_norm.add_forward(h, pending, row_map=batch.want_rows)
         with self.ctx.section("head"):
             return self.head(normed, out_dtype=torch.float32)

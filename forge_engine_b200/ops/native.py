@@ -54,9 +54,17 @@ def lib() -> ctypes.CDLL:
 
 
 def _declare(handle: ctypes.CDLL) -> None:
-    p, i, f = c_void_p, c_int, c_float
+    p, i, f, ll = c_void_p, c_int, c_float, ctypes.c_longlong
     signatures = {
-        "fe_embedding": [p, p, i, p, i, i, i, p, p],
+        "fe_embedding": [p, p, i, p, i, i, i, f, i, p, p],
+        "fe_stream_mix_norm": [p, i, p, i, f, p, p, p, i, p, f, p, i, p, i, i, i, p],
+        "fe_act_mul": [p, i, p, i, i, i, i, p],
+        "fe_gated_rmsnorm": [p, p, i, i, p, p, i, i, i, f, p],
+        "fe_qkv_prepare": [p, i, i, i, i, i, i, p, i, p, i, i, i, i, i, p, i, p, i, i, i, f, p, i, i, p, ll, ll, i,
+                           p, p, i, p, i, i, i, p, p, i, p, p],
+        "fe_attention_general": [p, ll, ll, p, i, i, p, i, i, p, ll, ll, i, p, i, i, i, i, i, p, p, p, i, f, i, p, p],
+        "fe_linear_recurrence": [p, i, i, i, i, i, i, p, p, p, p, p, i, i, i, i, i, p],
+        "fe_gemm_simt_batched": [p, i, p, i, p, i, i, i, i, i, ll, ll, ll, ll, ll, p],
         "fe_add_rmsnorm": [p, p, i, p, p, i, p, i, i, f, i, p],
         "fe_silu_mul": [p, p, i, i, i, i, p],
         "fe_qk_rope_cache": [p, i, p, p, f, p, p, i, p, p, p, p, p, i, i, i, i, i, i, i, i, p, p],
@@ -224,15 +232,254 @@ def _dense(t: torch.Tensor, name: str) -> torch.Tensor:
 # ---------------------------------------------------------------------------
 
 
-def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
-    """out[n] = float(table[ids[n]]); out is the 32-bit residual stream [N, H]."""
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, status: torch.Tensor,
+              scale: float = 1.0) -> None:
+    """out[n] = float(table[ids[n]]) * scale; out is the 32-bit residual stream [N, H], or
+    [N, S, H] for S copies of it (every copy gets the same row)."""
     _dense(ids, "ids"), _dense(table, "table"), _dense(out, "out")
     assert ids.dtype == torch.int32 and out.dtype == torch.float32
-    n, hidden = out.shape
+    n, hidden = out.shape[0], out.shape[-1]
+    copies = out.shape[1] if out.dim() == 3 else 1
+    assert table.shape[1] == hidden
     check(
         lib().fe_embedding(ptr(ids), ptr(table), code(table), ptr(out), n, hidden, table.shape[0],
-                           ptr(status), stream()),
+                           float(scale), int(copies), ptr(status), stream()),
         "embedding",
+    )
+
+
+NORM_NONE, NORM_RMS, NORM_LAYER = 0, 1, 2
+MAX_STREAMS = 8
+
+
+def stream_mix_norm(
+    streams: torch.Tensor,
+    update: torch.Tensor | None,
+    update_scale: float,
+    mix: torch.Tensor | None,
+    out_coef: torch.Tensor | None,
+    in_coef: torch.Tensor | None,
+    norm_kind: int,
+    weight: torch.Tensor | None,
+    eps: float,
+    out: torch.Tensor | None,
+    row_map: torch.Tensor | None = None,
+    write_streams: bool = True,
+) -> None:
+    """One launch over the residual streams [N, S, W] (32-bit; [N, W] is S = 1):
+    x'_t = sum_s mix[s, t] x_s + update_scale * out_coef[t] * update (only with ``update``;
+    ``mix`` None is the identity, ``out_coef`` None ones), written back unless
+    ``write_streams`` is false; u = sum_t in_coef[t] x'_t (None: ones); ``out`` = norm(u) *
+    weight (``NORM_RMS``, ``NORM_LAYER`` - mean taken off, variance as the mean squared
+    deviation - or ``NORM_NONE``: u itself).  ``out`` None only updates the streams.  With
+    ``row_map`` row r of ``out`` comes from token ``row_map[r]``."""
+    _dense(streams, "streams")
+    assert streams.dtype == torch.float32
+    n, width = streams.shape[0], streams.shape[-1]
+    count = streams.shape[1] if streams.dim() == 3 else 1
+    if update is not None:
+        _dense(update, "update")
+        assert update.shape == (n, width)
+    for name, t, numel in (("mix", mix, count * count), ("out_coef", out_coef, count), ("in_coef", in_coef, count),
+                           ("weight", weight, width)):
+        assert t is None or (t.dtype == torch.float32 and t.is_cuda and t.is_contiguous() and t.numel() == numel), name
+    rows = n if row_map is None else row_map.numel()
+    if out is not None:
+        _dense(out, "out")
+        assert out.shape == (rows, width)
+    assert row_map is None or row_map.dtype == torch.int32
+    check(
+        lib().fe_stream_mix_norm(
+            ptr(streams), count, ptr(update), code(update) if update is not None else F32, float(update_scale),
+            ptr(mix), ptr(out_coef), ptr(in_coef), int(norm_kind), ptr(weight), float(eps), ptr(out),
+            code(out) if out is not None else F32, ptr(row_map), rows, width, 1 if write_streams else 0, stream(),
+        ),
+        "stream_mix_norm",
+    )
+
+
+ACT_SILU, ACT_GELU_TANH = 0, 1
+
+
+def act_mul(gate_up: torch.Tensor, out: torch.Tensor, act: int) -> None:
+    """out[n, i] = act(gate_up[n, i]) * gate_up[n, inter + i] in 32-bit, rounded on store."""
+    _dense(gate_up, "gate_up"), _dense(out, "out")
+    rows, inter = out.shape
+    assert gate_up.shape == (rows, 2 * inter)
+    check(lib().fe_act_mul(ptr(gate_up), code(gate_up), ptr(out), code(out), rows, inter, int(act), stream()), "act_mul")
+
+
+def gated_rmsnorm(x: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float) -> None:
+    """out = x / sqrt(mean(x^2) + eps) * weight * sigmoid(gate); x is 32-bit [N, C]; ``gate``
+    [N, C] may be a column slice of a wider contiguous tensor."""
+    _dense(x, "x"), _dense(out, "out")
+    rows, size = x.shape
+    assert x.dtype == torch.float32 and weight.dtype == torch.float32 and weight.numel() == size
+    assert gate.shape == (rows, size) and gate.stride(1) == 1 and out.shape == (rows, size)
+    check(lib().fe_gated_rmsnorm(ptr(x), ptr(gate), code(gate), int(gate.stride(0)) if rows > 1 else size, ptr(weight),
+                                 ptr(out), code(out), rows, size, float(eps), stream()), "gated_rmsnorm")
+
+
+PREP_NORM_NONE, PREP_NORM_HEAD, PREP_NORM_WHOLE = 0, 1, 2
+
+
+def qkv_prepare(
+    *,
+    q: torch.Tensor | None,
+    q_heads: int = 0,
+    q_dim: int = 0,
+    q_norm: tuple = (PREP_NORM_NONE, 0, None),
+    q_rot_off: int = 0,
+    q_head_stride: int = 0,
+    q_out: torch.Tensor | None = None,
+    q_out_strides: tuple = (0, 0),
+    q_out_offset: int = 0,
+    k: torch.Tensor | None = None,
+    k_heads: int = 0,
+    k_dim: int = 0,
+    k_norm: tuple = (PREP_NORM_NONE, 0, None),
+    k_rot_off: int = 0,
+    v: torch.Tensor | None = None,
+    v_dim: int = 0,
+    eps: float = 0.0,
+    table: torch.Tensor | None = None,
+    rot_dims: int = 0,
+    interleaved: bool = False,
+    k_cache: torch.Tensor | None = None,
+    v_cache: torch.Tensor | None = None,
+    block_table: torch.Tensor | None = None,
+    positions: torch.Tensor,
+    token_entry: torch.Tensor,
+    status: torch.Tensor,
+) -> None:
+    """Normalise, rotate and store one step's queries, keys and values (all optional).
+
+    ``q`` [N, >= q_heads * q_dim] and ``k``, ``v`` may be column slices of one contiguous
+    projection output (row stride taken from the tensor).  ``q_norm`` / ``k_norm`` =
+    (mode, leading elements of a head that are normalised, 32-bit weight): per head or over
+    the whole projection.  ``table`` [N, rot_dims / 2, 2] holds cosine and sine of the
+    tokens' angles; elements [rot_off, rot_off + rot_dims) of every head are rotated (a
+    negative ``rot_off`` leaves that side as it is), neighbours paired when ``interleaved``,
+    else element j with j + rot_dims / 2.  Head h of a query token starts ``q_head_stride``
+    elements after head h - 1 (0: ``q_dim``).  Queries
+    go to ``q_out`` at token * q_out_strides[0] + head * q_out_strides[1] + q_out_offset,
+    keys and values into the pages of ``k_cache`` / ``v_cache``
+    [pages, k_heads, page_size, k_dim | v_dim]."""
+    n = positions.numel()
+    source = q if q is not None else k
+    assert source is not None and positions.dtype == torch.int32 and token_entry.dtype == torch.int32
+    for t in (q, k, v):
+        assert t is None or (t.is_cuda and t.stride(1) == 1 and t.shape[0] == n and t.dtype == source.dtype)
+    cache_dtype = q_out if q_out is not None else k_cache
+    if k is not None:
+        _dense(k_cache, "k_cache"), _dense(block_table, "block_table")
+        assert k_cache.shape[1] == k_heads and k_cache.shape[3] == k_dim
+        assert v is None or (v_cache is not None and v_cache.shape[3] == v_dim and v_cache.dtype == k_cache.dtype)
+    assert table is None or (table.dtype == torch.float32 and table.is_contiguous() and table.shape == (n, rot_dims // 2, 2))
+    for mode, dims, w in (q_norm, k_norm):
+        assert w is None or (w.dtype == torch.float32 and w.is_cuda and w.is_contiguous())
+        assert mode == PREP_NORM_NONE or w is not None
+    stride = lambda t: 0 if t is None else int(t.stride(0)) if n > 1 else int(t.shape[1])  # noqa: E731
+    pages = 0 if k_cache is None else k_cache.shape[0]
+    check(
+        lib().fe_qkv_prepare(
+            ptr(q), stride(q), int(q_head_stride), int(q_heads), int(q_dim), int(q_norm[0]), int(q_norm[1]), ptr(q_norm[2]), int(q_rot_off),
+            ptr(k), stride(k), int(k_heads), int(k_dim), int(k_norm[0]), int(k_norm[1]), ptr(k_norm[2]), int(k_rot_off),
+            ptr(v), stride(v), int(v_dim), code(source), float(eps), ptr(table), int(rot_dims if table is not None else 0),
+            1 if interleaved else 0, ptr(q_out), int(q_out_strides[0]), int(q_out_strides[1]), int(q_out_offset),
+            ptr(k_cache), ptr(v_cache), code(cache_dtype), ptr(block_table),
+            0 if block_table is None else block_table.shape[1], 0 if k_cache is None else k_cache.shape[2], pages,
+            ptr(positions), ptr(token_entry), n, ptr(status), stream(),
+        ),
+        "qkv_prepare",
+    )
+
+
+def attention_general(
+    q: torch.Tensor,
+    q_strides: tuple,
+    k_cache: torch.Tensor,
+    k_dim: int,
+    v_cache: torch.Tensor,
+    v_dim: int,
+    out: torch.Tensor,
+    o_strides: tuple,
+    block_table: torch.Tensor,
+    positions: torch.Tensor,
+    token_entry: torch.Tensor,
+    num_q_heads: int,
+    slopes: torch.Tensor | None,
+    window: int | None,
+    scale: float,
+    status: torch.Tensor,
+) -> None:
+    """Paged causal attention in 32-bit arithmetic for any key and value size.
+
+    Row (token, head) of ``q`` starts ``token * q_strides[0] + head * q_strides[1]`` elements
+    into it, likewise for ``out``.  ``k_cache`` is [pages, kv_heads, page_size, row]; the key
+    is the first ``k_dim`` elements of a row, the value the first ``v_dim`` of ``v_cache``'s
+    row (``v_cache`` may be ``k_cache`` itself: one cached vector that is key and value).
+    ``slopes`` (per query head, 32-bit) takes slope * (query position - key position) off
+    every score; ``window`` keeps the query's own and the window - 1 keys before it."""
+    num_pages, nkv, page_size, k_row = k_cache.shape
+    v_row = v_cache.shape[3]
+    n = positions.numel()
+    assert q.dtype == k_cache.dtype == v_cache.dtype == out.dtype
+    assert slopes is None or (slopes.dtype == torch.float32 and slopes.numel() == num_q_heads and slopes.is_cuda)
+    check(
+        lib().fe_attention_general(
+            ptr(q), int(q_strides[0]), int(q_strides[1]), ptr(k_cache), k_row, int(k_dim), ptr(v_cache), v_row,
+            int(v_dim), ptr(out), int(o_strides[0]), int(o_strides[1]), code(q), ptr(block_table),
+            block_table.shape[1], page_size, num_pages, nkv, int(num_q_heads), ptr(positions), ptr(token_entry),
+            ptr(slopes), int(window or 0), float(scale), n, ptr(status), stream(),
+        ),
+        "attention_general",
+    )
+
+
+def linear_recurrence(
+    proj: torch.Tensor,
+    q_off: int,
+    k_off: int,
+    v_off: int,
+    act: int,
+    state: torch.Tensor,
+    slots: torch.Tensor,
+    cu_tokens: torch.Tensor,
+    decay: torch.Tensor,
+    out: torch.Tensor,
+    entries: int,
+) -> None:
+    """S = decay_h S + k v^T, o = S^T q token by token for every entry of the step, from and
+    to the 32-bit ``state`` [slots, heads, dk, dv] rows named by ``slots``.  q, k, v are
+    act(columns of ``proj``) starting at ``q_off``, ``k_off`` (heads x dk each) and ``v_off``
+    (heads x dv); ``act`` ACT_SILU or -1 for none.  ``out`` 32-bit [N, heads * dv]."""
+    _dense(proj, "proj"), _dense(state, "state"), _dense(out, "out")
+    rows, heads, dk, dv = state.shape
+    assert state.dtype == torch.float32 and out.dtype == torch.float32 and decay.dtype == torch.float32
+    assert decay.numel() == heads and out.shape == (proj.shape[0], heads * dv)
+    assert slots.dtype == torch.int32 and cu_tokens.dtype == torch.int32
+    check(
+        lib().fe_linear_recurrence(ptr(proj), code(proj), int(proj.shape[1]), int(q_off), int(k_off), int(v_off),
+                                   int(act), ptr(state), ptr(slots), ptr(cu_tokens), ptr(decay), ptr(out),
+                                   int(entries), heads, dk, dv, rows, stream()),
+        "linear_recurrence",
+    )
+
+
+def gemm_simt_batched(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[n, b, :] = x[n, b, :] @ w[b].T with plain 32-bit FMAs, for x [n, batch, k] and out
+    [n, batch, o] that may be strided in their first two extents, and w [batch, o, k]
+    contiguous."""
+    _dense(w, "w")
+    n, batch, k = x.shape
+    o = w.shape[1]
+    assert w.shape == (batch, o, k) and out.shape == (n, batch, o) and x.stride(2) == 1 and out.stride(2) == 1
+    check(
+        lib().fe_gemm_simt_batched(ptr(x), code(x), ptr(w), code(w), ptr(out), code(out), n, o, k, batch,
+                                   int(x.stride(0)), int(out.stride(0)), int(x.stride(1)), o * k, int(out.stride(1)),
+                                   stream()),
+        "gemm_simt_batched",
     )
 
 

@@ -15,7 +15,8 @@ import os
 import torch
 
 from ..cache.manager import CacheNeeds, PagedKVSpec
-from ..errors import UnsupportedShapeError
+from ..config.specs import local_name
+from ..errors import ConfigError, UnsupportedShapeError
 from ..ops import native
 from .base import BuildContext, CacheView, Mixer, WeightInfo, build_part, register_part
 from .linear import Linear, fused_rows
@@ -126,58 +127,80 @@ class GQAttention(Mixer):
         """The kernels here are; a position encoding that rewrites q and k itself decides."""
         return bool(getattr(self.position, "graph_safe", False))
 
+    @staticmethod
+    def _is_general(spec) -> bool:
+        """Whether the layer needs what only the general kernels do: values of another size
+        than keys, q and k normalised over the whole projection, a bias on the distance."""
+        return (getattr(spec, "v_head_dim", None) not in (None, spec.head_dim)
+                or (spec.qk_norm and getattr(spec, "qk_norm_scope", "head") == "whole")
+                or getattr(spec, "distance_bias_base", None) is not None)
+
     def __init__(self, spec, weights: dict, ctx: BuildContext) -> None:
-        if spec.head_dim % 16 or spec.head_dim > 256:
+        self.general = self._is_general(spec)
+        if not self.general and (spec.head_dim % 16 or spec.head_dim > 256):
             raise UnsupportedShapeError(
                 f"head_dim={spec.head_dim}: the attention kernels take multiples of 16 up to 256"
             )
         if spec.num_heads % spec.num_kv_heads:
             raise UnsupportedShapeError("num_heads must be a multiple of num_kv_heads")
+        if getattr(spec, "qk_norm_scope", "head") not in ("head", "whole"):
+            raise ConfigError(f"qk_norm_scope={spec.qk_norm_scope!r}; known: head, whole")
         self.spec = spec
         self.ctx = ctx
         self.nq, self.nkv, self.d = spec.num_heads, spec.num_kv_heads, spec.head_dim
+        self.dv = getattr(spec, "v_head_dim", None) or self.d
+        name = lambda canonical: local_name(spec, canonical)  # noqa: E731
         bias = None
-        rows = [self.nq * self.d, self.nkv * self.d, self.nkv * self.d]
+        rows = [self.nq * self.d, self.nkv * self.d, self.nkv * self.dv]
         if spec.bias:
-            bias = fused_rows(weights, ["q_proj.bias", "k_proj.bias", "v_proj.bias"], rows)
+            bias = fused_rows(weights, [name("q_proj.bias"), name("k_proj.bias"), name("v_proj.bias")], rows)
         # q, k and v are looked up one at a time and copied into the fused tensor
         self.qkv_proj = Linear(
-            fused_rows(weights, ["q_proj.weight", "k_proj.weight", "v_proj.weight"], rows),
+            fused_rows(weights, [name("q_proj.weight"), name("k_proj.weight"), name("v_proj.weight")], rows),
             bias,
             status=ctx.status,
         )
-        self.o_proj = Linear(weights["o_proj.weight"], weights["o_proj.bias"] if spec.bias else None,
+        self.o_proj = Linear(weights[name("o_proj.weight")], weights[name("o_proj.bias")] if spec.bias else None,
                              status=ctx.status)
         self.q_norm = self.k_norm = None
         if spec.qk_norm:
-            self.q_norm = weights["q_norm.weight"].float().contiguous()
-            self.k_norm = weights["k_norm.weight"].float().contiguous()
+            self.q_norm = weights[name("q_norm.weight")].float().contiguous()
+            self.k_norm = weights[name("k_norm.weight")].float().contiguous()
         self.position = build_part(spec.position, {}, ctx)
+        self.slopes = None
+        base = getattr(spec, "distance_bias_base", None)
+        if base is not None:
+            heads = torch.arange(1, self.nq + 1, dtype=torch.float64)
+            self.slopes = (float(base) ** (-heads / self.nq)).float().to(ctx.device).contiguous()
         self._slots = None
         self.plan_key = ("gqa_attention", self.nq, self.nkv, self.d, spec.window)
         self.last_splits = None   # what the last step's decode entries ran with (0: balanced kernel)
 
     @classmethod
     def weight_shapes(cls, spec) -> dict:
+        dv = getattr(spec, "v_head_dim", None) or spec.head_dim
         q, kv, h = spec.num_heads * spec.head_dim, spec.num_kv_heads * spec.head_dim, spec.hidden_size
+        name = lambda canonical: local_name(spec, canonical)  # noqa: E731
         shapes = {
-            "q_proj.weight": WeightInfo((q, h)),
-            "k_proj.weight": WeightInfo((kv, h)),
-            "v_proj.weight": WeightInfo((kv, h)),
-            "o_proj.weight": WeightInfo((h, q)),
+            name("q_proj.weight"): WeightInfo((q, h)),
+            name("k_proj.weight"): WeightInfo((kv, h)),
+            name("v_proj.weight"): WeightInfo((spec.num_kv_heads * dv, h)),
+            name("o_proj.weight"): WeightInfo((h, spec.num_heads * dv)),
         }
         if spec.qk_norm:
-            shapes["q_norm.weight"] = WeightInfo((spec.head_dim,), "norm")
-            shapes["k_norm.weight"] = WeightInfo((spec.head_dim,), "norm")
+            whole = getattr(spec, "qk_norm_scope", "head") == "whole"
+            shapes[name("q_norm.weight")] = WeightInfo((q if whole else spec.head_dim,), "norm")
+            shapes[name("k_norm.weight")] = WeightInfo((kv if whole else spec.head_dim,), "norm")
         if spec.bias:
-            shapes["q_proj.bias"] = WeightInfo((q,), "bias")
-            shapes["k_proj.bias"] = WeightInfo((kv,), "bias")
-            shapes["v_proj.bias"] = WeightInfo((kv,), "bias")
-            shapes["o_proj.bias"] = WeightInfo((h,), "bias")
+            shapes[name("q_proj.bias")] = WeightInfo((q,), "bias")
+            shapes[name("k_proj.bias")] = WeightInfo((kv,), "bias")
+            shapes[name("v_proj.bias")] = WeightInfo((spec.num_kv_heads * dv,), "bias")
+            shapes[name("o_proj.bias")] = WeightInfo((h,), "bias")
         return shapes
 
     def cache_needs(self) -> CacheNeeds:
-        return CacheNeeds(kv=PagedKVSpec(self.nkv, self.d, self.spec.window))
+        return CacheNeeds(kv=PagedKVSpec(self.nkv, self.d, self.spec.window,
+                                         None if self.dv == self.d else self.dv))
 
     def decode_slots(self) -> int:
         """Blocks of the decode kernels this device holds at once: what the balanced kernel
@@ -205,6 +228,8 @@ class GQAttention(Mixer):
     def attend(self, x, batch, cache: CacheView):
         """Everything but the output projection: the heads' outputs [N, heads * head_dim]
         (a block that fuses ``o_proj`` with what follows takes them from here)."""
+        if self.general:
+            return self._attend_general(x, batch, cache)
         with self.ctx.section("mixer.qkv_rope_cache"):
             qkv = self._project(x, batch, cache)
         k_cache, v_cache = cache.kv
@@ -219,6 +244,43 @@ class GQAttention(Mixer):
                     qkv, qkv.shape[1], k_cache, v_cache, table, batch.positions, batch.token_entry,
                     self.spec.window, self.spec.scale, out, self.nq, self.ctx.status,
                 )
+        return out
+
+    def _attend_general(self, x, batch, cache: CacheView):
+        """The layer in its general form.  The projection's 32-bit sums go to one kernel that
+        normalises q and k (per head, or over the whole projection), rotates them if the
+        position encoding is a rotation, and stores k and v in their pages; the attention
+        kernel takes the distance bias and any key and value size."""
+        n = x.shape[0]
+        nq, nkv, d, dv = self.nq, self.nkv, self.d, self.dv
+        k_cache, v_cache = cache.kv
+        table = batch.group_tables[cache.group]
+        with self.ctx.section("mixer.qkv_rope_cache"):
+            qkv = self.qkv_proj(x, out_dtype=torch.float32)
+            rotary = self.position.rotary()
+            angles, rot_dims = None, 0
+            if rotary is None:
+                self.position.apply(qkv, nq, nkv, d, batch)
+            else:
+                angles, rot_dims = self.position.table(batch), rotary[1]
+            mode = native.PREP_NORM_NONE
+            if self.spec.qk_norm:
+                mode = native.PREP_NORM_WHOLE if self.spec.qk_norm_scope == "whole" else native.PREP_NORM_HEAD
+            q = torch.empty((n, nq * d), dtype=k_cache.dtype, device=x.device)
+            q_end, k_end = nq * d, (nq + nkv) * d
+            native.qkv_prepare(
+                q=qkv[:, :q_end], q_heads=nq, q_dim=d, q_norm=(mode, d, self.q_norm), q_out=q, q_out_strides=(nq * d, d),
+                k=qkv[:, q_end:k_end] if cache.owns else None, k_heads=nkv, k_dim=d, k_norm=(mode, d, self.k_norm),
+                v=qkv[:, k_end:] if cache.owns else None, v_dim=dv, eps=self.spec.qk_norm_eps,
+                table=angles, rot_dims=rot_dims, interleaved=getattr(self.position, "interleaved", False),
+                k_cache=k_cache, v_cache=v_cache, block_table=table, positions=batch.positions,
+                token_entry=batch.token_entry, status=self.ctx.status,
+            )
+        out = torch.empty((n, nq * dv), dtype=k_cache.dtype, device=x.device)
+        with self.ctx.section("mixer.attention"):
+            native.attention_general(q, (nq * d, d), k_cache, d, v_cache, dv, out, (nq * dv, dv), table,
+                                     batch.positions, batch.token_entry, nq, self.slopes, self.spec.window,
+                                     self.spec.scale, self.ctx.status)
         return out
 
     def _project(self, x, batch, cache: CacheView):
@@ -297,7 +359,7 @@ class GQAttention(Mixer):
         rest the prefill kernel; both may run in one step.  (run prefill, run decode, splits
         of the decode kernel - 0: the kernel that spreads all tiles evenly) under this
         mixer's key; layers with the same geometry share it."""
-        if self.ctx.dtype != torch.bfloat16 or self.plan_key in plans:
+        if self.ctx.dtype != torch.bfloat16 or self.plan_key in plans or self.general:
             return
         groups = self.nq // self.nkv
         limit = native.ATTN_DECODE_ROWS

@@ -52,7 +52,8 @@ class WeightInfo:
     """Shape and role of one tensor; the role picks the random initialiser."""
 
     shape: tuple
-    role: str = "matrix"  # "matrix" N(0, std) | "norm" 1 + N(0, 0.1) | "bias" N(0, std)
+    # "matrix" N(0, std) | "norm" 1 + N(0, 0.1) | "bias" N(0, std) | "identity" I + N(0, 0.1)
+    role: str = "matrix"
 
 
 @dataclass

@@ -4,6 +4,9 @@
 h += mixer(norm1(h)); h += ffn(norm2(h)).  The residual stream ``h`` is a 32-bit
 tensor updated in place; the block returns its last update *unadded* so that the next
 block's first norm (or the final norm) adds it in the same kernel that normalises.
+
+"stream_mix" is the same pre-norm block over several copies of the residual stream that
+learned weights mix (or over one, with the update scaled by a constant).
 """
 
 from __future__ import annotations
@@ -13,7 +16,7 @@ import os
 import torch
 
 from ..ops import native
-from .base import BuildContext, CacheView, build_part, part_class, register_arrangement
+from .base import BuildContext, CacheView, WeightInfo, build_part, part_class, register_arrangement
 
 
 class PreNormBlock:
@@ -108,4 +111,98 @@ class PreNormBlock:
             return self.ffn.forward(normed)
 
 
+class StreamMixBlock:
+    """Pre-norm sublayers over several copies of the residual stream.
+
+    The stream ``h`` is 32-bit [N, S, hidden].  A sublayer (the mixer; then the feed-forward,
+    if the layer has one) reads u = sum_s in[s] x_s through its norm and writes back
+    x_t = sum_s mix[s, t] x_s + c out[t] y for all t at once, c being the spec's
+    ``update_scale``.  With ``learned`` false there is one stream and in = out = mix = 1:
+    the plain x += c y.  Adding a sublayer's output and normalising for the next one is one
+    kernel launch; the block hands its last output on, unadded, as ``(y, mix, out, c)``, and
+    ``close`` folds the last one of the model into the final norm of the summed streams."""
+
+    roles = ("input_norm", "mixer", "post_norm", "ffn", "mix1", "mix2")
+
+    def __init__(self, spec, weights: dict, ctx: BuildContext) -> None:
+        self.ctx = ctx
+        self.options = spec.options
+        self.scale = float(spec.options.update_scale)
+        self.input_norm = build_part(spec.input_norm, weights["input_norm"], ctx)
+        self.mixer = build_part(spec.mixer, weights["mixer"], ctx)
+        self.ffn = self.post_norm = None
+        if spec.ffn is not None:
+            self.post_norm = build_part(spec.post_norm, weights["post_norm"], ctx)
+            self.ffn = build_part(spec.ffn, weights["ffn"], ctx)
+        self.coefficients = [(None, None, None), (None, None, None)]      # (in, out, mix) per sublayer
+        if spec.options.learned:
+            for index, role in enumerate(("mix1", "mix2")):
+                if role in weights:
+                    part = weights[role]
+                    self.coefficients[index] = tuple(
+                        part[key].to(device=ctx.device, dtype=torch.float32).contiguous() for key in ("in", "out", "mix"))
+
+    @classmethod
+    def weight_shapes(cls, spec) -> dict:
+        """role -> {local name -> WeightInfo}"""
+        streams = spec.options.streams
+        mixing = {"in": WeightInfo((streams,), "norm"), "out": WeightInfo((streams,), "norm"),
+                  "mix": WeightInfo((streams, streams), "identity")}
+        shapes = {"input_norm": part_class(spec.input_norm).weight_shapes(spec.input_norm),
+                  "mixer": part_class(spec.mixer).weight_shapes(spec.mixer)}
+        if spec.options.learned:
+            shapes["mix1"] = dict(mixing)
+        if spec.ffn is not None:
+            shapes["post_norm"] = part_class(spec.post_norm).weight_shapes(spec.post_norm)
+            shapes["ffn"] = part_class(spec.ffn).weight_shapes(spec.ffn)
+            if spec.options.learned:
+                shapes["mix2"] = dict(mixing)
+        return shapes
+
+    def cache_needs(self):
+        return self.mixer.cache_needs()
+
+    def plan_step(self, entries: list, page_size: int, plans: dict) -> None:
+        planner = getattr(self.mixer, "plan_step", None)
+        if planner is not None:
+            planner(entries, page_size, plans)
+
+    @property
+    def graph_safe(self) -> bool:
+        parts = [self.input_norm, self.mixer] + ([self.post_norm, self.ffn] if self.ffn is not None else [])
+        return all(getattr(part, "graph_safe", False) for part in parts)
+
+    def _enter(self, h, pending, sublayer: int, norm):
+        """Add what is pending, mix, and normalise the sublayer's input."""
+        update, mix, out, scale = pending if pending is not None else (None, None, None, 1.0)
+        normed = torch.empty((h.shape[0], h.shape[-1]), dtype=self.ctx.dtype, device=h.device)
+        native.stream_mix_norm(h, update, scale, mix, out, self.coefficients[sublayer][0], norm.stream_kind,
+                               norm.weight, norm.eps, normed)
+        return normed
+
+    def forward(self, h, pending, batch, cache: CacheView):
+        with self.ctx.section("input_norm"):
+            normed = self._enter(h, pending, 0, self.input_norm)
+        with self.ctx.section("mixer"):
+            update = self.mixer.forward(normed, batch, cache)
+        pending = (update, self.coefficients[0][2], self.coefficients[0][1], self.scale)
+        if self.ffn is None:
+            return pending
+        with self.ctx.section("post_norm"):
+            normed = self._enter(h, pending, 1, self.post_norm)
+        with self.ctx.section("ffn"):
+            update = self.ffn.forward(normed)
+        return (update, self.coefficients[1][2], self.coefficients[1][1], self.scale)
+
+    def close(self, h, pending, final_norm, row_map):
+        """The model's last step: what is pending is added, the streams are summed, and the
+        final norm is taken - for the rows of ``row_map`` only, without writing the streams."""
+        update, mix, out, scale = pending if pending is not None else (None, None, None, 1.0)
+        normed = torch.empty((row_map.numel(), h.shape[-1]), dtype=self.ctx.dtype, device=h.device)
+        native.stream_mix_norm(h, update, scale, mix, out, None, final_norm.stream_kind, final_norm.weight,
+                               final_norm.eps, normed, row_map, write_streams=False)
+        return normed
+
+
 register_arrangement("pre_norm", PreNormBlock, replace=True)
+register_arrangement("stream_mix", StreamMixBlock, replace=True)

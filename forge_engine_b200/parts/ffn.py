@@ -1,43 +1,49 @@
-"""Gated feed-forward: down(silu(gate(x)) * up(x)) (src/forge_engine/qwen3.py:210-227).
+"""Gated feed-forward: down(act(gate(x)) * up(x)) with act = SiLU
+(src/forge_engine/qwen3.py:210-227) or the tanh form of GELU.
 gate and up are one fused projection; the activation product is one kernel."""
 
 from __future__ import annotations
 
 import torch
 
+from ..config.specs import local_name
 from ..errors import ConfigError
 from ..ops import native
 from .base import BuildContext, FeedForward, WeightInfo, register_part
 from .linear import Linear, fused_rows, interleaved_rows
 
 GATE_UP_BLOCK = 16
+ACTIVATIONS = {"silu": native.ACT_SILU, "gelu_tanh": native.ACT_GELU_TANH}
 
 
 class GatedMLP(FeedForward):
     graph_safe = True
 
     def __init__(self, spec, weights: dict, ctx: BuildContext) -> None:
-        if spec.activation != "silu":
-            raise ConfigError(f"activation {spec.activation!r} is not implemented (silu only)")
+        if spec.activation not in ACTIVATIONS:
+            raise ConfigError(f"activation {spec.activation!r} is not implemented; known: {', '.join(ACTIVATIONS)}")
+        self.activation = ACTIVATIONS[spec.activation]
         self.inter = spec.intermediate_size
+        gate, up, down = (local_name(spec, n) for n in ("gate_proj.weight", "up_proj.weight", "down_proj.weight"))
         # Rows of the fused weight alternate 16 gate and 16 up features where the size allows:
-        # the tensor-core kernel then finishes silu(gate) * up in its epilogue.
-        self.block = GATE_UP_BLOCK if self.inter % GATE_UP_BLOCK == 0 else 0
+        # the tensor-core kernel then finishes silu(gate) * up in its epilogue.  (Only SiLU
+        # has that epilogue; another activation keeps gate and up rows apart.)
+        self.block = GATE_UP_BLOCK if self.inter % GATE_UP_BLOCK == 0 and self.activation == native.ACT_SILU else 0
         # the sources are looked up one at a time and copied into the fused tensor
         if self.block:
-            fused = interleaved_rows(weights, "gate_proj.weight", "up_proj.weight", self.inter, self.block)
+            fused = interleaved_rows(weights, gate, up, self.inter, self.block)
         else:
-            fused = fused_rows(weights, ["gate_proj.weight", "up_proj.weight"], [self.inter, self.inter])
+            fused = fused_rows(weights, [gate, up], [self.inter, self.inter])
         self.gate_up = Linear(fused, status=ctx.status)
-        self.down = Linear(weights["down_proj.weight"], status=ctx.status)
+        self.down = Linear(weights[down], status=ctx.status)
 
     @classmethod
     def weight_shapes(cls, spec) -> dict:
         h, i = spec.hidden_size, spec.intermediate_size
         return {
-            "gate_proj.weight": WeightInfo((i, h)),
-            "up_proj.weight": WeightInfo((i, h)),
-            "down_proj.weight": WeightInfo((h, i)),
+            local_name(spec, "gate_proj.weight"): WeightInfo((i, h)),
+            local_name(spec, "up_proj.weight"): WeightInfo((i, h)),
+            local_name(spec, "down_proj.weight"): WeightInfo((h, i)),
         }
 
     def forward_add(self, x, residual) -> bool:
@@ -51,9 +57,12 @@ class GatedMLP(FeedForward):
     def forward(self, x):
         act = self.gate_up.silu_mul(x, self.block) if self.block else None
         if act is None:
-            gate_up = self.gate_up(x)
             act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
-            native.silu_mul(gate_up, act, self.block)
+            if self.activation == native.ACT_SILU:
+                native.silu_mul(self.gate_up(x), act, self.block)
+            else:
+                # the activation is taken of the 32-bit sums of the projection, not of their rounding
+                native.act_mul(self.gate_up(x, out_dtype=torch.float32), act, self.activation)
         return self.down(act)
 
 

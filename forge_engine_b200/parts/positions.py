@@ -21,8 +21,16 @@ class RotaryEncoding(PositionEncoding):
             raise ValueError("rotary_dim must be even and at most head_dim")
         self.rotary_dim = spec.rotary_dim
         self.theta = float(spec.theta)
-        exponent = torch.arange(0, spec.rotary_dim, 2, dtype=torch.float32) / spec.rotary_dim
-        self.inv_freq = (1.0 / (spec.theta**exponent)).to(ctx.device).contiguous()
+        # which elements form a pair is the business of the kernel that rotates; the angles
+        # are the same either way
+        self.interleaved = bool(getattr(spec, "interleaved", False))
+        if self.interleaved:
+            # theta^(-2j / rotary_dim) worked out in 64-bit and rounded once
+            exponent = torch.arange(0, spec.rotary_dim, 2, dtype=torch.float64) / spec.rotary_dim
+            self.inv_freq = (self.theta ** -exponent).float().to(ctx.device).contiguous()
+        else:
+            exponent = torch.arange(0, spec.rotary_dim, 2, dtype=torch.float32) / spec.rotary_dim
+            self.inv_freq = (1.0 / (spec.theta**exponent)).to(ctx.device).contiguous()
 
     def rotary(self):
         return self.inv_freq, self.rotary_dim

@@ -186,7 +186,7 @@ def open_checkpoint(
                 if shape != tuple(expected[name].shape):
                     wrong.append(f"{name}: stored {shape}, model needs {tuple(expected[name].shape)}")
                 stored = _stored_dtype(handle, name)
-                if getattr(expected[name], "role", "matrix") in ("matrix", "norm", "bias") and stored not in _FLOAT_NAMES:
+                if getattr(expected[name], "role", "matrix") in ("matrix", "norm", "bias", "identity") and stored not in _FLOAT_NAMES:
                     wrong_dtype.append(f"{name}: stored as {stored}, a floating-point tensor is needed")
     if missing or unexpected or wrong or wrong_dtype:
         lines = [f"checkpoint in {folder} does not match the model:"]

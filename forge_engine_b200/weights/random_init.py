@@ -3,7 +3,8 @@
 Upstream has no such mode (its tests rely on torch's default initialisers,
 tests/test_qwen3.py:48-49).  Here matrices and biases are N(0, std), norm weights are
 1 + N(0, 0.1).  Every tensor is drawn from a generator of its own, seeded with the model's
-seed and the tensor's place in ``expected_tensors``, so a tensor's values do not depend on
+seed and the tensor's place in ``expected_tensors`` (a square mixing matrix is the identity
+plus N(0, 0.1)), so a tensor's values do not depend on
 which others were drawn before it: ``RandomTensors`` draws a tensor when the model asks
 for it (benchmark-sized models are assembled layer by layer and never exist twice).
 """
@@ -49,8 +50,11 @@ class RandomTensors(Mapping):
         for begin in range(0, max(1, flat.numel()), self.PIECE):
             count = min(self.PIECE, flat.numel() - begin)
             noise = torch.randn(count, generator=generator, dtype=torch.float32, device=self.device)
-            flat[begin : begin + count] = noise.mul_(0.1).add_(1.0) if info.role == "norm" else noise.mul_(self.std)
+            flat[begin : begin + count] = (noise.mul_(0.1).add_(1.0) if info.role == "norm"
+                                           else noise.mul_(0.1) if info.role == "identity" else noise.mul_(self.std))
             del noise
+        if info.role == "identity":
+            out.add_(torch.eye(info.shape[0], info.shape[1], dtype=self.dtype, device=self.device))
         return out
 
     def close(self) -> None:
