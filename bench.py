@@ -521,6 +521,158 @@ def chain_timeline(tokens: int) -> int:
     return 0
 
 
+# Layer sizes for `--design-compare`: the Zofadra mixers beside the Qwen3 layer at the same
+# width, feed-forward size and head counts (random weights; a few layers of one kind each).
+DESIGN_SIZES = {
+    "2560": {"width": 2560, "ff": 9728, "heads": 32, "kv_heads": 8, "dim": 128, "window": 1024,
+             "latent": {"dim": 64, "rot_dim": 32, "vdim": 64, "q_rank": 768, "kv_rank": 256},
+             "recurrence": {"dim": 64, "vdim": 64}},
+    "4096": {"width": 4096, "ff": 12288, "heads": 32, "kv_heads": 8, "dim": 128, "window": 1024,
+             "latent": {"dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": 1536, "kv_rank": 448},
+             "recurrence": {"dim": 128, "vdim": 128}},
+}
+
+
+def design_compare(args) -> int:
+    """Prefill (one 2,048-token prompt) and decode (batch 8, 2,048-token contexts) of models
+    of `--layers` (4) layers of one kind: the Qwen3 layer, and the Zofadra attention, latent
+    attention and linear-recurrence layers at the same sizes, plus a model that mixes them.
+    One JSON line per model: tokens/s, ms per step, the median device time of every part of a
+    step (CUDA events round each part, in a second runner) and, for the token-mixing kernel,
+    its share of the measured peaks (prefill: its flops over the library GEMM's burst rate;
+    decode: the cache or state bytes it must move over the copy bandwidth)."""
+    import torch
+
+    from forge_engine_b200.engine import ModelRunner, StepEntry
+    from forge_engine_b200.ops import native
+
+    hbm_gbs, bf16_tflops, peak_source = peaks()
+    layers = args.layers or 4
+    batch, vocab = args.batch, 32000
+    torch.cuda.set_device(0)
+    gen = torch.Generator().manual_seed(5)
+    sizes = sorted(DESIGN_SIZES) if args.design_compare == "all" else [args.design_compare]
+    for size in sizes:
+        z = DESIGN_SIZES[size]
+        W, H, G, D, window = z["width"], z["heads"], z["kv_heads"], z["dim"], z["window"]
+        lat, rec = z["latent"], z["recurrence"]
+        mlp = {"kind": "dense", "ff": z["ff"]}
+        attention = {"type": "attention", "mlp": mlp, "mixer": {
+            "heads": H, "kv_heads": G, "dim": D, "vdim": D, "scale": D ** -0.5, "mask": {"size": window}}}
+        latent = {"type": "latent_attention", "mlp": mlp, "mixer": dict(
+            lat, heads=H, rot={"base": 1e6, "dims": lat["rot_dim"]}, scale=(lat["dim"] + lat["rot_dim"]) ** -0.5)}
+        recurrence = {"type": "lightning", "mlp": mlp, "mixer": dict(
+            rec, heads=H, decay=[1.0 - 2.0 ** (-5 - 3 * h / H) for h in range(H)])}
+        shared = {"type": "latent_attention", "mlp": mlp, "mixer": dict(latent["mixer"], kv_from=0)}
+
+        def zofadra(kinds):
+            return {"architecture": "Zofadra", "vocab": vocab, "width": W, "norm": {"eps": 1e-5}, "streams": 2,
+                    "residual_mult": 0.5, "embedding": {"scale": 1.0}, "layers": kinds}
+
+        models = {
+            "qwen3": dict(CONFIG_4B, vocab_size=vocab, hidden_size=W, intermediate_size=z["ff"], num_hidden_layers=layers,
+                          num_attention_heads=H, num_key_value_heads=G, head_dim=D, tie_word_embeddings=False),
+            "qwen3-window": dict(CONFIG_4B, vocab_size=vocab, hidden_size=W, intermediate_size=z["ff"],
+                                 num_hidden_layers=layers, num_attention_heads=H, num_key_value_heads=G, head_dim=D,
+                                 tie_word_embeddings=False, sliding_window=window, use_sliding_window=True,
+                                 max_window_layers=0),
+            "zofadra-attention": zofadra([attention] * layers),
+            "zofadra-latent": zofadra([latent] * layers),
+            "zofadra-recurrence": zofadra([recurrence] * layers),
+            "zofadra-mixed": zofadra([latent, attention, recurrence, shared, attention][:max(layers, 5)]),
+        }
+        rank, rot = lat["kv_rank"], lat["rot_dim"]
+        seen = lambda span: sum(min(i + 1, span) for i in range(CONTEXT))          # noqa: E731  keys all queries see
+        mixer_cost = {     # (flops of a 2,048-token prompt, bytes a decode step must move) per layer
+            "qwen3": (4 * H * D * seen(CONTEXT), batch * CONTEXT * G * 2 * D * 2),
+            "qwen3-window": (4 * H * D * seen(window), batch * window * G * 2 * D * 2),
+            "zofadra-attention": (4 * H * D * seen(window), batch * window * G * 2 * D * 2),
+            "zofadra-latent": (2 * H * (2 * rank + rot) * seen(CONTEXT), batch * CONTEXT * (rank + rot) * 2),
+            "zofadra-recurrence": (4 * H * rec["dim"] * rec["vdim"] * CONTEXT, batch * H * rec["dim"] * rec["vdim"] * 4 * 2),
+        }
+        mixer_part = {"qwen3": "mixer.attention", "qwen3-window": "mixer.attention", "zofadra-attention": "mixer.attention",
+                      "zofadra-latent": "mixer.attention", "zofadra-recurrence": "mixer.recurrence"}
+        for name, raw in models.items():
+            n_layers = len(raw["layers"]) if "layers" in raw else raw["num_hidden_layers"]
+            pages = batch * (-(-(CONTEXT + 64) // PAGE) + 1) + -(-CONTEXT // PAGE) + 8
+            plain = ModelRunner.from_random(raw, 0, dtype="bfloat16", page_size=PAGE, num_pages=pages,
+                                            max_requests=batch + 1, std=0.02)
+            timed = ModelRunner(plain.model, page_size=PAGE, num_pages=pages, max_requests=batch + 1, timing=True)
+            prompt = torch.randint(0, vocab, (CONTEXT,), generator=gen).tolist()
+            ids = torch.randint(0, vocab, (batch,), generator=gen).tolist()
+            result = {"design_compare": name, "width": W, "layers": n_layers, "batch": batch, "context": CONTEXT,
+                      "dtype": "bf16", "data": "synthetic", "peaks": peak_source}
+            for runner in (plain, timed):
+                runner.model.ctx.timer = runner.timer
+                for group in runner.cache.groups:
+                    group.storage.normal_(0.0, 1.0)
+                times = []
+                for i in range(3 + 5):
+                    runner.begin(f"p{i}")
+                    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    torch.cuda.synchronize()
+                    begin.record()
+                    runner.step([StepEntry(f"p{i}", prompt, [CONTEXT - 1])])
+                    end.record()
+                    torch.cuda.synchronize()
+                    times.append(begin.elapsed_time(end))
+                    runner.end(f"p{i}")
+                    if runner is timed and i == 2:
+                        runner.timings(reset=True)
+                if runner is plain:
+                    result["prefill_ms"] = round(statistics.median(times[3:]), 3)
+                    result["prefill_tok_s"] = round(CONTEXT / statistics.median(times[3:]) * 1e3, 1)
+                else:
+                    parts = runner.timings(reset=True)["parts"]
+                    result["prefill_parts_ms"] = {k: round(v["median"], 4) for k, v in parts.items()}
+                keys = [f"d{i}" for i in range(batch)]
+                for key in keys:
+                    runner.begin(key)
+                    runner.cache.reserve(key, CONTEXT)
+                    runner.cache.advance(key, CONTEXT)
+                steps = 40
+                for _ in range(args.warmup):
+                    runner.step([StepEntry(k, [t], [0]) for k, t in zip(keys, ids)])
+                if runner is timed:
+                    runner.timings(reset=True)
+                sampler = ClockSampler()
+                sampler.start()
+                begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                begin.record()
+                for _ in range(steps):
+                    runner.step([StepEntry(k, [t], [0]) for k, t in zip(keys, ids)])
+                end.record()
+                torch.cuda.synchronize()
+                clocks = sampler.stop()
+                runner.check_status()
+                for key in keys:
+                    runner.end(key)
+                if runner is plain:
+                    ms = begin.elapsed_time(end) / steps
+                    result["decode_ms_per_step"] = round(ms, 4)
+                    result["decode_tok_s"] = round(batch / ms * 1e3, 1)
+                    result["clocks"] = clocks
+                else:
+                    parts = runner.timings(reset=True)["parts"]
+                    result["decode_parts_ms"] = {k: round(v["median"], 4) for k, v in parts.items()}
+            if name in mixer_cost:
+                flops, moved = mixer_cost[name]
+                part = mixer_part[name]
+                result["mixer_kernel"] = {
+                    "part": part,
+                    "prefill_ms": result["prefill_parts_ms"].get(part),
+                    "prefill_frac_of_gemm_peak": round(flops / (result["prefill_parts_ms"][part] * 1e-3) / (bf16_tflops * 1e12), 4),
+                    "decode_ms": result["decode_parts_ms"].get(part),
+                    "decode_frac_of_copy_peak": round(moved / (result["decode_parts_ms"][part] * 1e-3) / (hbm_gbs * 1e9), 4),
+                }
+            plain.model.ctx.timer = None
+            print(json.dumps(result), flush=True)
+            del plain, timed
+            torch.cuda.empty_cache()
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -551,6 +703,8 @@ def main() -> int:
     parser.add_argument("--mixed-only", type=int, metavar="TOKENS",
                         help="only the mixed step: 8 requests decoding beside a prompt portion, TOKENS tokens in all "
                              "(with --kernel-times: the kernels of one such step)")
+    parser.add_argument("--design-compare", metavar="WIDTH", choices=sorted(DESIGN_SIZES) + ["all"],
+                        help="prefill and decode of the Zofadra layer kinds beside the Qwen3 layer at equal size")
     parser.add_argument("--kernel-times", action="store_true",
                         help="also print the device time of every kernel of one more step (for profiles/)")
     args = parser.parse_args()
@@ -565,6 +719,8 @@ def main() -> int:
         print(f"bench.py measures one GPU; --gpus {args.gpus} is not supported by this single-GPU engine")
         return 2
     args.warmup = max(3, args.warmup)
+    if args.design_compare:
+        return design_compare(args)
     if args.workload:
         return scheduler_workload(args.workload, args.layers)
     if args.kernels:

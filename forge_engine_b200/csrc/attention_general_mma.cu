@@ -1,0 +1,378 @@
+// Tensor-core form of the general paged attention (bfloat16), compiled once per shape:
+//   -DFE_DK=<key size> -DFE_DV=<value size> -DFE_V_IN_K=<0|1>
+// FE_V_IN_K = 1: the value is the first FE_DV elements of the cached key row (a latent that is
+// key and value at once); then no second tile is loaded.
+//
+// A block of 4 warps owns 64 rows - the (token, query head) pairs of one entry that share one
+// kv head, token-major - and walks the key tiles its rows can see (causal, optional window),
+// cp.async double-buffered from the cache pages.  S = Q K^T and O += P V run on mma.sync
+// m16n8k16 with 32-bit accumulators; scale, distance bias, mask and the online softmax are
+// 32-bit.  The weights P enter the second product as a sum of two bfloat16 numbers (the
+// rounded weight and the rounded remainder), so they carry 16 bits of mantissa and not 8.
+// Few rows and many keys (decoding): `splits` blocks share a row tile's key tiles and leave
+// (sum, maximum, normaliser) in a workspace that a second kernel combines.
+#include "attention_common.cuh"
+
+#ifndef FE_DK
+#error "compile with -DFE_DK=... -DFE_DV=... -DFE_V_IN_K=..."
+#endif
+
+#define GM_CAT2(a, b, c, d) a##b##_##c##_##d
+#define GM_CAT(a, b, c, d) GM_CAT2(a, b, c, d)
+#define GM_NAME(base) GM_CAT(base, FE_DK, FE_DV, FE_V_IN_K)
+
+namespace {
+
+constexpr int DK = FE_DK, DV = FE_DV;
+constexpr bool V_IN_K = FE_V_IN_K != 0;
+constexpr int BM = 64, WARPS = 4;
+constexpr int BN = DK > 320 ? 32 : 64;
+constexpr int KS = DK + 8;                     // row stride of the Q and K tiles in shared memory
+constexpr int VS = DV + 8;
+constexpr int QC = DK / 8, VC = DV / 8;        // 16-byte pieces per row
+constexpr int K_TILE = BN * KS, V_TILE = V_IN_K ? 0 : BN * VS;
+constexpr size_t SMEM_BYTES = sizeof(bf16) * (size_t)(BM * KS + 2 * K_TILE + 2 * V_TILE);
+
+struct Params {
+  const bf16* q; long long q_ts, q_hs;
+  const bf16* k; int k_row;
+  const bf16* v; int v_row;
+  bf16* out; long long o_ts, o_hs;
+  const int* table; int max_pages, page_size, num_pages, nkv, groups;
+  const int* cu_tokens; const int* starts;
+  const float* slopes; int window; float scale;
+  int splits; int tiles; float* part;
+};
+
+__device__ __forceinline__ unsigned smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr(dst)), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldsm4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void ldsm4_trans(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void mma16816(float* c, const unsigned* a, unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack2(float x, float y) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
+  return *reinterpret_cast<const unsigned*>(&h);
+}
+// the rounded pair and the rounded remainders
+__device__ __forceinline__ void split2(float x, float y, unsigned& hi, unsigned& lo) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
+  const float2 back = __bfloat1622float2(h);
+  hi = *reinterpret_cast<const unsigned*>(&h);
+  lo = pack2(x - back.x, y - back.y);
+}
+
+__global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(Params p, int* status) {
+  extern __shared__ __align__(16) unsigned char raw[];
+  bf16* Qs = reinterpret_cast<bf16*>(raw);
+  bf16* Ks = Qs + BM * KS;
+  bf16* Vs = Ks + 2 * K_TILE;
+  pdl_trigger();
+  pdl_wait();
+  const int tile = blockIdx.x / p.splits, split = blockIdx.x - tile * p.splits;
+  const int entry = blockIdx.y, kvh = blockIdx.z;
+  const int t_begin = p.cu_tokens[entry];
+  const int count = p.cu_tokens[entry + 1] - t_begin;
+  const int start = p.starts[entry];
+  const int rows_total = count * p.groups;
+  const int row0 = tile * BM;
+  if (row0 >= rows_total) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int* table = p.table + (size_t)entry * p.max_pages;
+
+  // the row tile of Q
+  for (int idx = tid; idx < BM * QC; idx += WARPS * 32) {
+    const int r = idx / QC, c = idx - r * QC;
+    const int rho = row0 + r;
+    uint4 value = make_uint4(0, 0, 0, 0);
+    if (rho < rows_total) {
+      const int token = t_begin + rho / p.groups, head = kvh * p.groups + rho % p.groups;
+      value = *reinterpret_cast<const uint4*>(p.q + (size_t)token * p.q_ts + (size_t)head * p.q_hs + c * 8);
+    }
+    *reinterpret_cast<uint4*>(Qs + r * KS + c * 8) = value;
+  }
+
+  const int tok_lo = row0 / p.groups, tok_hi = min(count - 1, (row0 + BM - 1) / p.groups);
+  const int key_hi = start + tok_hi;                                        // last key any row sees
+  const int key_lo = p.window > 0 ? max(0, start + tok_lo - p.window + 1) : 0;
+  const int kt_lo = key_lo / BN, kt_hi = key_hi / BN + 1;
+  const int per = (kt_hi - kt_lo + p.splits - 1) / p.splits;
+  const int my_lo = kt_lo + split * per, my_hi = min(kt_hi, my_lo + per);
+
+  auto load_tile = [&](int kt, int stage) {
+    bf16* kd = Ks + stage * K_TILE;
+    for (int idx = tid; idx < BN * QC; idx += WARPS * 32) {
+      const int r = idx / QC, c = idx - r * QC;
+      const int key = kt * BN + r;
+      bool valid = key >= key_lo && key <= key_hi;
+      const bf16* src = p.k;
+      if (valid) {
+        const int logical = key / p.page_size;
+        const int page = logical < p.max_pages ? table[logical] : -1;
+        if (page < 0 || page >= p.num_pages) {
+          valid = false;                     // a page the window has given back: its keys are masked anyway
+        } else {
+          src = p.k + (((size_t)page * p.nkv + kvh) * p.page_size + (key - logical * p.page_size)) * p.k_row + c * 8;
+        }
+      }
+      cp_async16(kd + r * KS + c * 8, src, valid);
+    }
+    if constexpr (!V_IN_K) {
+      bf16* vd = Vs + stage * V_TILE;
+      for (int idx = tid; idx < BN * VC; idx += WARPS * 32) {
+        const int r = idx / VC, c = idx - r * VC;
+        const int key = kt * BN + r;
+        bool valid = key >= key_lo && key <= key_hi;
+        const bf16* src = p.v;
+        if (valid) {
+          const int logical = key / p.page_size;
+          const int page = logical < p.max_pages ? table[logical] : -1;
+          if (page < 0 || page >= p.num_pages) {
+            valid = false;
+          } else {
+            src = p.v + (((size_t)page * p.nkv + kvh) * p.page_size + (key - logical * p.page_size)) * p.v_row + c * 8;
+          }
+        }
+        cp_async16(vd + r * VS + c * 8, src, valid);
+      }
+    }
+  };
+
+  // this thread's two rows: r_a = lane / 4 and r_a + 8 of the warp's sixteen
+  const int quad = lane >> 2, pair = lane & 3;
+  int row_pos[2];
+  float row_slope[2];
+  bool row_live[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int rho = row0 + warp * 16 + quad + 8 * h;
+    row_live[h] = rho < rows_total;
+    row_pos[h] = row_live[h] ? start + rho / p.groups : -1;
+    row_slope[h] = (row_live[h] && p.slopes) ? p.slopes[kvh * p.groups + rho % p.groups] : 0.f;
+  }
+  float o[DV / 8][4];
+#pragma unroll
+  for (int n = 0; n < DV / 8; ++n)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) o[n][c] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+  if (my_lo < my_hi) {
+    load_tile(my_lo, 0);
+    cp_commit();
+  }
+  for (int kt = my_lo; kt < my_hi; ++kt) {
+    const int stage = (kt - my_lo) & 1;
+    if (kt + 1 < my_hi) {
+      load_tile(kt + 1, stage ^ 1);
+      cp_commit();
+      cp_wait<1>();
+    } else {
+      cp_wait<0>();
+    }
+    __syncthreads();
+    const bf16* kd = Ks + stage * K_TILE;
+    const bf16* vd = V_IN_K ? kd : Vs + stage * V_TILE;
+    constexpr int vstride = V_IN_K ? KS : VS;
+
+    float s[BN / 8][4];
+#pragma unroll
+    for (int j = 0; j < BN / 8; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) s[j][c] = 0.f;
+#pragma unroll 2
+    for (int kk = 0; kk < DK / 16; ++kk) {
+      unsigned a[4];
+      ldsm4(a[0], a[1], a[2], a[3], Qs + (warp * 16 + (lane & 15)) * KS + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+      for (int j = 0; j < BN / 8; j += 2) {
+        unsigned b0, b1, b2, b3;
+        ldsm4(b0, b1, b2, b3, kd + ((j + (lane >> 4)) * 8 + (lane & 7)) * KS + kk * 16 + ((lane >> 3) & 1) * 8);
+        mma16816(s[j], a, b0, b1);
+        mma16816(s[j + 1], a, b2, b3);
+      }
+    }
+
+    // scale, bias, mask; running maximum and normaliser
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < BN / 8; ++j) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int h = c >> 1;
+        const int key = kt * BN + j * 8 + pair * 2 + (c & 1);
+        const bool visible = row_live[h] && key <= row_pos[h] && (p.window <= 0 || key > row_pos[h] - p.window);
+        const float sc = visible ? s[j][c] * p.scale - row_slope[h] * (float)(row_pos[h] - key) : -INFINITY;
+        s[j][c] = sc;
+        mx[h] = fmaxf(mx[h], sc);
+      }
+    }
+    float corr[2], base[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+      const float m_new = fmaxf(m_run[h], mx[h]);
+      base[h] = m_new == -INFINITY ? 0.f : m_new;
+      corr[h] = expf(m_run[h] - base[h]);
+      m_run[h] = m_new;
+      l_run[h] *= corr[h];
+    }
+#pragma unroll
+    for (int j = 0; j < BN / 8; ++j) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float w = expf(s[j][c] - base[c >> 1]);
+        s[j][c] = w;
+        l_run[c >> 1] += w;
+      }
+    }
+#pragma unroll
+    for (int n = 0; n < DV / 8; ++n) {
+      o[n][0] *= corr[0]; o[n][1] *= corr[0];
+      o[n][2] *= corr[1]; o[n][3] *= corr[1];
+    }
+
+    // O += P V, P as rounded weight + rounded remainder
+#pragma unroll
+    for (int ks = 0; ks < BN / 16; ++ks) {
+      unsigned hi[4], lo[4];
+      split2(s[2 * ks][0], s[2 * ks][1], hi[0], lo[0]);
+      split2(s[2 * ks][2], s[2 * ks][3], hi[1], lo[1]);
+      split2(s[2 * ks + 1][0], s[2 * ks + 1][1], hi[2], lo[2]);
+      split2(s[2 * ks + 1][2], s[2 * ks + 1][3], hi[3], lo[3]);
+#pragma unroll
+      for (int n = 0; n < DV / 8; n += 2) {
+        unsigned b0, b1, b2, b3;
+        ldsm4_trans(b0, b1, b2, b3, vd + (ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * vstride + (n + (lane >> 4)) * 8);
+        mma16816(o[n], hi, b0, b1);
+        mma16816(o[n], lo, b0, b1);
+        mma16816(o[n + 1], hi, b2, b3);
+        mma16816(o[n + 1], lo, b2, b3);
+      }
+    }
+    __syncthreads();
+  }
+
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+  }
+  if (p.splits == 1) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      if (!row_live[h]) continue;
+      const int rho = row0 + warp * 16 + quad + 8 * h;
+      const int token = t_begin + rho / p.groups, head = kvh * p.groups + rho % p.groups;
+      bf16* dst = p.out + (size_t)token * p.o_ts + (size_t)head * p.o_hs;
+      const float inv = l_run[h] > 0.f ? 1.f / l_run[h] : 0.f;
+#pragma unroll
+      for (int n = 0; n < DV / 8; ++n)
+        *reinterpret_cast<__nv_bfloat162*>(dst + n * 8 + pair * 2) =
+            __floats2bfloat162_rn(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);
+    }
+    return;
+  }
+  // partial result of this split: [entry][tile][kvh][split][row][DV + 2]
+  float* mine = p.part + ((((size_t)entry * p.tiles + tile) * p.nkv + kvh) * p.splits + split) * (size_t)BM * (DV + 2);
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = warp * 16 + quad + 8 * h;
+    float* dst = mine + (size_t)r * (DV + 2);
+#pragma unroll
+    for (int n = 0; n < DV / 8; ++n) {
+      dst[n * 8 + pair * 2] = o[n][2 * h];
+      dst[n * 8 + pair * 2 + 1] = o[n][2 * h + 1];
+    }
+    if (pair == 0) {
+      dst[DV] = m_run[h];
+      dst[DV + 1] = l_run[h];
+    }
+  }
+}
+
+__global__ void __launch_bounds__(128) attention_mma_merge_kernel(Params p) {
+  pdl_trigger();
+  pdl_wait();
+  const int tile = blockIdx.x, entry = blockIdx.y, kvh = blockIdx.z;
+  const int t_begin = p.cu_tokens[entry];
+  const int rows_total = (p.cu_tokens[entry + 1] - t_begin) * p.groups;
+  const int row0 = tile * BM;
+  if (row0 >= rows_total) return;
+  const float* base = p.part + (((size_t)entry * p.tiles + tile) * p.nkv + kvh) * p.splits * (size_t)BM * (DV + 2);
+  const int rows = min(BM, rows_total - row0);
+  for (int idx = threadIdx.x; idx < rows * DV; idx += blockDim.x) {
+    const int r = idx / DV, d = idx - r * DV;
+    float big = -INFINITY;
+    for (int s = 0; s < p.splits; ++s) big = fmaxf(big, base[((size_t)s * BM + r) * (DV + 2) + DV]);
+    float num = 0.f, den = 0.f;
+    for (int s = 0; s < p.splits; ++s) {
+      const float* row = base + ((size_t)s * BM + r) * (DV + 2);
+      const float f = row[DV] == -INFINITY ? 0.f : expf(row[DV] - big);
+      num = fmaf(row[d], f, num);
+      den = fmaf(row[DV + 1], f, den);
+    }
+    const int rho = row0 + r;
+    const int token = t_begin + rho / p.groups, head = kvh * p.groups + rho % p.groups;
+    p.out[(size_t)token * p.o_ts + (size_t)head * p.o_hs + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+  }
+}
+
+}  // namespace
+
+// Floats of workspace a launch with these sizes needs (0 for one split).
+FE_EXPORT long long GM_NAME(fe_attention_gmma_workspace_)(int entries, int max_new, int groups, int nkv, int splits) {
+  if (splits <= 1) return 0;
+  const long long tiles = ((long long)max_new * groups + BM - 1) / BM;
+  return (long long)entries * tiles * nkv * splits * BM * (DV + 2);
+}
+
+FE_EXPORT int GM_NAME(fe_attention_gmma_)(const void* q, long long q_ts, long long q_hs, const void* k_cache, int k_row,
+                                          const void* v_cache, int v_row, void* out, long long o_ts, long long o_hs,
+                                          const int* block_table, int max_pages, int page_size, int num_pages, int nkv,
+                                          int num_q_heads, const int* cu_tokens, const int* starts, int entries,
+                                          int max_new, const float* slopes, int window, float scale, int splits,
+                                          float* workspace, int* status, cudaStream_t stream) {
+  if (entries <= 0 || max_new <= 0) return 0;
+  if (nkv < 1 || num_q_heads % nkv || nkv > 65535 || entries > 65535) return FE_ERR_BAD_SHAPE;
+  if (k_row % 8 || v_row % 8 || q_ts % 8 || q_hs % 8 || o_ts % 2 || o_hs % 2) return FE_ERR_BAD_ALIGN;
+  if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) % 16 || (uintptr_t)out % 4) return FE_ERR_BAD_ALIGN;
+  if (splits < 1) splits = 1;
+  if (splits > 1 && workspace == nullptr) return FE_ERR_BAD_SHAPE;
+  const int groups = num_q_heads / nkv;
+  const int tiles = (int)(((long long)max_new * groups + BM - 1) / BM);
+  Params p{(const bf16*)q, q_ts, q_hs, (const bf16*)k_cache, k_row, (const bf16*)v_cache, v_row, (bf16*)out, o_ts, o_hs,
+           block_table, max_pages, page_size, num_pages, nkv, groups, cu_tokens, starts, slopes, window, scale,
+           splits, tiles, workspace};
+  static bool configured = false;
+  if (!configured) {
+    const cudaError_t rc = cudaFuncSetAttribute(attention_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+    if (rc != cudaSuccess) return (int)rc;
+    configured = true;
+  }
+  dim3 grid((unsigned)tiles * splits, entries, nkv);
+  int rc = fe_launch_dependent(attention_mma_kernel, grid, dim3(WARPS * 32), SMEM_BYTES, stream, p, status);
+  if (rc) return rc;
+  if (splits > 1) {
+    rc = fe_launch_dependent(attention_mma_merge_kernel, dim3(tiles, entries, nkv), dim3(128), 0, stream, p);
+    if (rc) return rc;
+  }
+  return fe_last_error();
+}

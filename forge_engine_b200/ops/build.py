@@ -43,8 +43,12 @@ def find_nvcc() -> str:
 PER_HEAD_DIM = ("attention_mma.cu",)
 
 
+# Compiled once per (key size, value size, value-inside-key) of a general attention layer.
+PER_SHAPE = ("attention_general_mma.cu",)
+
+
 def _sources() -> list[Path]:
-    return sorted(p for p in CSRC.glob("*.cu") if p.name not in PER_HEAD_DIM)
+    return sorted(p for p in CSRC.glob("*.cu") if p.name not in PER_HEAD_DIM + PER_SHAPE)
 
 
 def _fingerprint(nvcc: str, sources: list, defines: list) -> str:
@@ -131,3 +135,13 @@ def attention_library_path(head_dim: int, verbose: bool = True) -> Path:
         raise CUDAUnavailableError(f"no tensor-core attention for head_dim={head_dim}")
     name = f"libforge_engine_b200_attn_d{head_dim}.so"
     return _build(name, [CSRC / n for n in PER_HEAD_DIM], [f"-DFE_HEAD_DIM={head_dim}"], verbose)
+
+
+def general_attention_library_path(key_dim: int, value_dim: int, value_in_key: bool, verbose: bool = True) -> Path:
+    """The tensor-core form of the general attention kernel for one shape."""
+    if key_dim % 16 or value_dim % 16 or key_dim < 16 or value_dim < 16:
+        raise CUDAUnavailableError(f"no tensor-core general attention for sizes {key_dim}, {value_dim}")
+    shared = 1 if value_in_key else 0
+    name = f"libforge_engine_b200_gattn_{key_dim}_{value_dim}_{shared}.so"
+    defines = [f"-DFE_DK={key_dim}", f"-DFE_DV={value_dim}", f"-DFE_V_IN_K={shared}"]
+    return _build(name, [CSRC / n for n in PER_SHAPE], defines, verbose)

@@ -14,7 +14,7 @@ from ctypes import c_float, c_int, c_ulonglong, c_void_p
 import torch
 
 from ..errors import CUDAUnavailableError, ForgeEngineError, UnsupportedShapeError
-from .build import attention_library_path, library_path
+from .build import attention_library_path, general_attention_library_path, library_path
 
 F32, BF16 = 0, 1
 _DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16}
@@ -395,6 +395,57 @@ def qkv_prepare(
     )
 
 
+_general_libs: dict = {}
+GENERAL_MMA_MAX_VALUE = 256     # accumulator registers of a warp's sixteen rows
+GENERAL_MMA_MAX_KEY = 576
+GENERAL_MMA_ROWS = 64           # (token, head) rows of one block
+
+
+def general_attention_lib(key_dim: int, value_dim: int, value_in_key: bool):
+    """(launcher, workspace size function) of the tensor-core general attention compiled for
+    one shape (built on first use)."""
+    key = (key_dim, value_dim, bool(value_in_key))
+    fns = _general_libs.get(key)
+    if fns is None:
+        path = general_attention_library_path(*key)
+        try:
+            handle = ctypes.CDLL(str(path))
+        except OSError as error:
+            raise CUDAUnavailableError(f"cannot load {path}: {error}") from error
+        suffix = f"{key_dim}_{value_dim}_{1 if value_in_key else 0}"
+        run = getattr(handle, f"fe_attention_gmma_{suffix}")
+        p, i, f, ll = c_void_p, c_int, c_float, ctypes.c_longlong
+        run.argtypes = [p, ll, ll, p, i, p, i, p, ll, ll, p, i, i, i, i, i, p, p, i, i, p, i, f, i, p, p, p]
+        run.restype = c_int
+        space = getattr(handle, f"fe_attention_gmma_workspace_{suffix}")
+        space.argtypes = [i, i, i, i, i]
+        space.restype = ll
+        fns = _general_libs[key] = (run, space, handle)
+    return fns[0], fns[1]
+
+
+def general_mma_takes(dtype, key_dim: int, value_dim: int) -> bool:
+    """Whether the tensor-core form of the general attention runs for these sizes."""
+    return (dtype == torch.bfloat16 and key_dim % 16 == 0 and value_dim % 16 == 0
+            and 16 <= key_dim <= GENERAL_MMA_MAX_KEY and 16 <= value_dim <= GENERAL_MMA_MAX_VALUE
+            and _os.environ.get("FORGE_ENGINE_GENERAL_MMA", "1") != "0")
+
+
+def general_splits(entries: list, groups: int, kv_heads: int, window: int | None, slots: int = 296) -> int:
+    """How many blocks share the keys of one row tile, for a step of ``entries`` ((slot,
+    cached, new) each).  Only steps whose entries all fit one row tile (decoding, short
+    portions) are split: enough blocks to fill the GPU once, each with at least two key
+    tiles of 64, a power of two up to 32."""
+    if not entries or any(count * groups > GENERAL_MMA_ROWS for _, _, count in entries):
+        return 1
+    longest = max(start + count for _, start, count in entries)
+    if window:
+        longest = min(longest, window + max(count for _, _, count in entries))
+    tiles = -(-longest // 64)
+    wish = min(slots // max(1, len(entries) * kv_heads), tiles // 2, 32)
+    return 1 if wish < 2 else 1 << (wish.bit_length() - 1)
+
+
 def attention_general(
     q: torch.Tensor,
     q_strides: tuple,
@@ -412,8 +463,14 @@ def attention_general(
     window: int | None,
     scale: float,
     status: torch.Tensor,
+    entries: tuple | None = None,
+    splits: int = 1,
 ) -> None:
-    """Paged causal attention in 32-bit arithmetic for any key and value size.
+    """Paged causal attention for any key and value size: scores, softmax and sums in 32-bit.
+
+    ``entries = (cu_tokens, starts, number of entries, most new tokens of an entry)`` lets
+    bfloat16 calls whose sizes are multiples of 16 run on the tensor-core kernel (``splits``
+    blocks per row tile share its keys); everything else runs the plain kernel.
 
     Row (token, head) of ``q`` starts ``token * q_strides[0] + head * q_strides[1]`` elements
     into it, likewise for ``out``.  ``k_cache`` is [pages, kv_heads, page_size, row]; the key
@@ -426,6 +483,25 @@ def attention_general(
     n = positions.numel()
     assert q.dtype == k_cache.dtype == v_cache.dtype == out.dtype
     assert slopes is None or (slopes.dtype == torch.float32 and slopes.numel() == num_q_heads and slopes.is_cuda)
+    value_in_key = v_cache.data_ptr() == k_cache.data_ptr()
+    if (entries is not None and general_mma_takes(q.dtype, k_dim, v_dim) and k_dim == k_row
+            and (value_in_key or v_dim == v_row) and all(s % 8 == 0 for s in (*q_strides, *o_strides))):
+        cu_tokens, starts, n_entries, max_new = entries
+        run, space = general_attention_lib(k_dim, v_dim, value_in_key)
+        groups = num_q_heads // nkv
+        floats = int(space(int(n_entries), int(max_new), groups, nkv, int(splits)))
+        workspace = _attention_workspace(q.device, floats) if floats else None
+        check(
+            run(ptr(q), int(q_strides[0]), int(q_strides[1]), ptr(k_cache), k_row, ptr(v_cache), v_row, ptr(out),
+                int(o_strides[0]), int(o_strides[1]), ptr(block_table), block_table.shape[1], page_size, num_pages, nkv,
+                int(num_q_heads), ptr(cu_tokens), ptr(starts), int(n_entries), int(max_new), ptr(slopes),
+                int(window or 0), float(scale), int(splits), ptr(workspace), ptr(status), stream()),
+            "attention_general (tensor cores)",
+        )
+        if splits > 1:
+            global LAUNCHES
+            LAUNCHES += 1
+        return
     check(
         lib().fe_attention_general(
             ptr(q), int(q_strides[0]), int(q_strides[1]), ptr(k_cache), k_row, int(k_dim), ptr(v_cache), v_row,

@@ -173,7 +173,7 @@ class GQAttention(Mixer):
             heads = torch.arange(1, self.nq + 1, dtype=torch.float64)
             self.slopes = (float(base) ** (-heads / self.nq)).float().to(ctx.device).contiguous()
         self._slots = None
-        self.plan_key = ("gqa_attention", self.nq, self.nkv, self.d, spec.window)
+        self.plan_key = ("gqa_attention", self.nq, self.nkv, self.d, spec.window) + (("general", self.dv) if self.general else ())
         self.last_splits = None   # what the last step's decode entries ran with (0: balanced kernel)
 
     @classmethod
@@ -277,10 +277,14 @@ class GQAttention(Mixer):
                 token_entry=batch.token_entry, status=self.ctx.status,
             )
         out = torch.empty((n, nq * dv), dtype=k_cache.dtype, device=x.device)
+        if self.plan_key not in batch.plans:
+            self.plan_step(batch.entries, k_cache.shape[2], batch.plans)
         with self.ctx.section("mixer.attention"):
             native.attention_general(q, (nq * d, d), k_cache, d, v_cache, dv, out, (nq * dv, dv), table,
                                      batch.positions, batch.token_entry, nq, self.slopes, self.spec.window,
-                                     self.spec.scale, self.ctx.status)
+                                     self.spec.scale, self.ctx.status,
+                                     entries=(batch.cu_tokens, batch.starts, batch.n_entries, batch.max_new),
+                                     splits=batch.plans[self.plan_key])
         return out
 
     def _project(self, x, batch, cache: CacheView):
@@ -359,7 +363,15 @@ class GQAttention(Mixer):
         rest the prefill kernel; both may run in one step.  (run prefill, run decode, splits
         of the decode kernel - 0: the kernel that spreads all tiles evenly) under this
         mixer's key; layers with the same geometry share it."""
-        if self.ctx.dtype != torch.bfloat16 or self.plan_key in plans or self.general:
+        if self.general:
+            # the general kernels: how many blocks share a row tile's keys
+            if self.plan_key not in plans:
+                splits = 1
+                if native.general_mma_takes(self.ctx.dtype, self.d, self.dv):
+                    splits = native.general_splits(entries, self.nq // self.nkv, self.nkv, self.spec.window)
+                plans[self.plan_key] = splits
+            return
+        if self.ctx.dtype != torch.bfloat16 or self.plan_key in plans:
             return
         groups = self.nq // self.nkv
         limit = native.ATTN_DECODE_ROWS

@@ -53,6 +53,16 @@ class LatentAttention(Mixer):
         self.o_proj = Linear(weights[name("o")], status=ctx.status)
         self.position = build_part(spec.position, {}, ctx)
         self.rot_dims = self.position.rotary()[1]
+        self.plan_key = ("latent_attention", self.h, self.kv_rank, self.r)
+
+    def plan_step(self, entries: list, page_size: int, plans: dict) -> None:
+        """The host's decision for a step of ``entries`` ((slot, cached, new) each): how many
+        blocks share the keys of one tile of query rows (layers of one geometry share it)."""
+        if self.plan_key not in plans:
+            splits = 1
+            if native.general_mma_takes(self.ctx.dtype, self.kv_rank + self.r, self.kv_rank):
+                splits = native.general_splits(entries, self.h, 1, None)
+            plans[self.plan_key] = splits
 
     @classmethod
     def weight_shapes(cls, spec) -> dict:
@@ -122,10 +132,14 @@ class LatentAttention(Mixer):
             # the other parts through the transposed key expansion
             self._per_head(q.view(n, h, d + r)[:, :, :d], self.uk_t, q_eff[:, :, :rank])
         mixed = torch.empty((n, h, rank), dtype=dtype, device=x.device)
+        if self.plan_key not in batch.plans:
+            self.plan_step(batch.entries, latent_cache.shape[2], batch.plans)
         with self.ctx.section("mixer.attention"):
             native.attention_general(q_eff, (h * (rank + r), rank + r), latent_cache, rank + r, latent_cache, rank,
                                      mixed, (h * rank, rank), table, batch.positions, batch.token_entry, h, None, None,
-                                     self.spec.scale, self.ctx.status)
+                                     self.spec.scale, self.ctx.status,
+                                     entries=(batch.cu_tokens, batch.starts, batch.n_entries, batch.max_new),
+                                     splits=batch.plans[self.plan_key])
         heads = torch.empty((n, h, dv), dtype=dtype, device=x.device)
         with self.ctx.section("mixer.expand"):
             self._per_head(mixed, self.uv, heads)

@@ -226,7 +226,7 @@ def seeded_weights(cfg: dict, seed: int) -> dict:
     return weights
 
 
-def latent_layer(heads=4, dim=16, rot_dim=8, vdim=16, q_rank=32, kv_rank=32, rot_dims=None, base=10000.0,
+def latent_layer(heads=4, dim=16, rot_dim=16, vdim=16, q_rank=32, kv_rank=32, rot_dims=None, base=10000.0,
                  kv_from=None, ff=64):
     m = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank,
          "rot": {"base": base, "dims": rot_dims or rot_dim}, "scale": (dim + rot_dim) ** -0.5}

@@ -274,9 +274,10 @@ def plain_attention(q, k, v, slopes, window, scale):
     return out
 
 
-def paged_attention(q, k, v, slopes, window, scale, dtype, new_tokens, page_size=4):
+def paged_attention(q, k, v, slopes, window, scale, dtype, new_tokens, page_size=4, splits=1):
     """Run attention_general for the last ``new_tokens`` queries over keys laid out in
-    shuffled pages."""
+    shuffled pages (bfloat16 with sizes in sixteens: the tensor-core kernel, ``splits`` blocks
+    sharing the keys)."""
     from forge_engine_b200.ops import native
 
     device = "cuda"
@@ -297,8 +298,10 @@ def paged_attention(q, k, v, slopes, window, scale, dtype, new_tokens, page_size
     qd = q[first:].to(dtype).to(device).contiguous()
     out = torch.empty(new_tokens, H, dv, dtype=dtype, device=device)
     sl = None if slopes is None else torch.tensor(slopes, dtype=torch.float32, device=device)
+    cu_tokens = torch.tensor([0, new_tokens], dtype=torch.int32, device=device)
+    starts = torch.tensor([first], dtype=torch.int32, device=device)
     native.attention_general(qd, (H * dk, dk), k_cache, dk, v_cache, dv, out, (H * dv, dv), table, positions, entry,
-                             H, sl, window, scale, status)
+                             H, sl, window, scale, status, entries=(cu_tokens, starts, 1, new_tokens), splits=splits)
     assert int(status.item()) == 0
     return out.float().cpu()
 
@@ -311,7 +314,7 @@ def test_keys_just_inside_and_just_outside_a_window(window, new_tokens, dtype):
     holds and the one before it.  One key too many or too few changes the result by the
     size of the values.  In a prompt (all queries at once) and decoding (one query)."""
     gen = torch.Generator().manual_seed(window)
-    T, H, G, dk, dv = 70, 4, 2, 16, 24
+    T, H, G, dk, dv = 70, 4, 2, 16, 32
     q = 0.1 * torch.randn(T, H, dk, generator=gen)
     k = 0.1 * torch.randn(T, G, dk, generator=gen)
     v = torch.randn(T, G, dv, generator=gen)
@@ -326,9 +329,10 @@ def test_keys_just_inside_and_just_outside_a_window(window, new_tokens, dtype):
     slopes = [2.0 ** (-8.0 * (h + 1) / H) for h in range(H)]
     ref = plain_attention(q, k, v, slopes, window, 0.5)
     count = new_tokens or T
-    got = paged_attention(q, k, v, slopes, window, 0.5, dtype, count)
     tol = 2e-5 if dtype == torch.float32 else 2e-2
-    assert float((got - ref[T - count :]).abs().max()) <= tol
+    for splits in (1, 2) if new_tokens else (1,):
+        got = paged_attention(q, k, v, slopes, window, 0.5, dtype, count, splits=splits)
+        assert float((got - ref[T - count :]).abs().max()) <= tol, splits
 
 
 @pytest.mark.parametrize("dtype", (torch.float32, torch.bfloat16))
@@ -337,7 +341,7 @@ def test_a_key_far_back_among_hundreds(new_tokens, dtype):
     """No window: one early key (also one at a page's last place and one at a page's first)
     outscores hundreds of later ones, for queries far away."""
     gen = torch.Generator().manual_seed(1)
-    T, H, G, dk, dv = 600, 2, 1, 24, 16
+    T, H, G, dk, dv = 600, 2, 1, 32, 16
     q = 0.05 * torch.randn(T, H, dk, generator=gen)
     k = 0.05 * torch.randn(T, G, dk, generator=gen)
     v = torch.randn(T, G, dv, generator=gen)
@@ -348,10 +352,46 @@ def test_a_key_far_back_among_hundreds(new_tokens, dtype):
     q, k, v = (t.to(torch.bfloat16).float() for t in (q, k, v))
     ref = plain_attention(q, k, v, None, None, 1.0)
     count = new_tokens or 200
-    got = paged_attention(q, k, v, None, None, 1.0, dtype, count)
     assert float((ref[-1, 0] - v[[2, 3, 4, 255][(T - 1) % 4], 0].double()).abs().max()) < 0.05   # the mark decides
     tol = 2e-5 if dtype == torch.float32 else 2e-2
-    assert float((got - ref[T - count :]).abs().max()) <= tol
+    for splits in (1, 4, 8) if new_tokens else (1,):
+        got = paged_attention(q, k, v, None, None, 1.0, dtype, count, splits=splits)
+        assert float((got - ref[T - count :]).abs().max()) <= tol, splits
+
+
+def test_tensor_core_attention_with_the_value_inside_the_key():
+    """One cached vector that is key and value (its first elements), many heads on one kv head,
+    queries and outputs with strides of their own; prompt portion and decoding, with splits."""
+    from forge_engine_b200.ops import native
+
+    gen = torch.Generator().manual_seed(9)
+    T, H, dk, dv, page = 333, 6, 48, 32, 8
+    q = torch.randn(T, H, dk, generator=gen).to(torch.bfloat16).float()
+    kv = torch.randn(T, 1, dk, generator=gen).to(torch.bfloat16).float()
+    ref = plain_attention(q, kv, kv[:, :, :dv], None, None, 0.2)
+    device = "cuda"
+    pages = -(-T // page)
+    order = torch.randperm(pages + 2, generator=gen)[:pages]
+    cache = torch.zeros(pages + 2, 1, page, dk, dtype=torch.bfloat16, device=device)
+    for t in range(T):
+        cache[order[t // page], 0, t % page] = kv[t, 0].to(torch.bfloat16).to(device)
+    table = order.to(torch.int32).view(1, pages).to(device)
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    for count, splits in ((T, 1), (100, 1), (1, 1), (1, 4), (3, 2)):
+        first = T - count
+        positions = torch.arange(first, T, dtype=torch.int32, device=device)
+        entry = torch.zeros(count, dtype=torch.int32, device=device)
+        wide = torch.zeros(count, H, dk + 16, dtype=torch.bfloat16, device=device)       # rows wider than the query
+        wide[:, :, :dk] = q[first:].to(torch.bfloat16).to(device)
+        out = torch.zeros(count, H, dv + 8, dtype=torch.bfloat16, device=device)
+        native.attention_general(wide, (H * (dk + 16), dk + 16), cache, dk, cache, dv, out, (H * (dv + 8), dv + 8), table,
+                                 positions, entry, H, None, None, 0.2, status,
+                                 entries=(torch.tensor([0, count], dtype=torch.int32, device=device),
+                                          torch.tensor([first], dtype=torch.int32, device=device), 1, count),
+                                 splits=splits)
+        assert int(status.item()) == 0
+        assert float((out[:, :, :dv].float().cpu() - ref[first:]).abs().max()) <= 2e-2, (count, splits)
+        assert float(out[:, :, dv:].abs().max()) == 0
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
