@@ -126,3 +126,190 @@ FE_EXPORT int fe_linear_recurrence(const void* proj, int dtype, int ld, int q_of
 #undef LAUNCH
   return rc ? rc : fe_last_error();
 }
+
+// ---------------------------------------------------------------------------
+// The same recurrence for long portions, chunk-parallel.  An entry's tokens are cut into
+// chunks of LC (from the entry's first token of this step).  With S the state before a
+// chunk and t, j counting inside it,
+//   o_t = sum_{j <= t} decay^(t - j) (q_t . k_j) v_j  +  decay^(t + 1) S^T q_t
+//   S'  = decay^len S + sum_j decay^(len - 1 - j) k_j v_j^T
+// Kernel 1 (a block per chunk and head) takes the first sum and the second line's sum;
+// kernel 2 walks an entry's chunks in order, element by element of the state, leaving every
+// chunk's incoming state where its sum was; kernel 3 (a block per chunk and head) adds the
+// state's share.  All products and sums are 32-bit.
+// ---------------------------------------------------------------------------
+#define LC 64
+
+// Which entry and which of its chunks a global chunk index is; false past the last one.
+__device__ __forceinline__ bool lr_locate(const int* cu_tokens, int entries, int chunk, int* entry, int* local,
+                                          int* first_chunk) {
+  int seen = 0;
+  for (int e = 0; e < entries; ++e) {
+    const int n = (cu_tokens[e + 1] - cu_tokens[e] + LC - 1) / LC;
+    if (chunk < seen + n) {
+      *entry = e;
+      *local = chunk - seen;
+      *first_chunk = seen;
+      return true;
+    }
+    seen += n;
+  }
+  return false;
+}
+
+template <typename TI>
+__global__ void __launch_bounds__(256)
+lr_chunk_local_kernel(const TI* __restrict__ proj, int ld, int q_off, int k_off, int v_off, int act,
+                      const int* __restrict__ cu_tokens, int entries, const float* __restrict__ decay,
+                      float* __restrict__ out, float* __restrict__ sums, int heads, int dk, int dv) {
+  extern __shared__ float smem[];
+  float* qs = smem;                       // [LC][dk + 1]
+  float* ks = qs + LC * (dk + 1);         // [LC][dk + 1]
+  float* vs = ks + LC * (dk + 1);         // [LC][dv]
+  float* as = vs + LC * dv;               // [LC][LC + 1]
+  float* pw = as + LC * (LC + 1);         // [LC + 1] powers of the decay
+  pdl_trigger();
+  pdl_wait();
+  int entry, local, first;
+  if (!lr_locate(cu_tokens, entries, blockIdx.x, &entry, &local, &first)) return;
+  const int head = blockIdx.y;
+  const int t0 = cu_tokens[entry] + local * LC;
+  const int len = min(LC, cu_tokens[entry + 1] - t0);
+  const float lam = decay[head];
+  for (int i = threadIdx.x; i <= LC; i += blockDim.x) pw[i] = (float)pow((double)lam, (double)i);
+  for (int i = threadIdx.x; i < len * dk; i += blockDim.x) {
+    const int t = i / dk, d = i - t * dk;
+    const TI* row = proj + (size_t)(t0 + t) * ld + (size_t)head * dk + d;
+    qs[t * (dk + 1) + d] = lr_act(to_float(row[q_off]), act);
+    ks[t * (dk + 1) + d] = lr_act(to_float(row[k_off]), act);
+  }
+  for (int i = threadIdx.x; i < len * dv; i += blockDim.x) {
+    const int t = i / dv, c = i - t * dv;
+    vs[i] = lr_act(to_float(proj[(size_t)(t0 + t) * ld + v_off + (size_t)head * dv + c]), act);
+  }
+  __syncthreads();
+  // weights of the chunk's own keys
+  for (int i = threadIdx.x; i < len * LC; i += blockDim.x) {
+    const int t = i / LC, j = i - t * LC;
+    float w = 0.f;
+    if (j <= t) {
+      const float* qt = qs + t * (dk + 1);
+      const float* kj = ks + j * (dk + 1);
+      for (int d = 0; d < dk; ++d) w = fmaf(qt[d], kj[d], w);
+      w *= pw[t - j];
+    }
+    as[t * (LC + 1) + j] = w;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < len * dv; i += blockDim.x) {
+    const int t = i / dv, c = i - t * dv;
+    float o = 0.f;
+    for (int j = 0; j <= t; ++j) o = fmaf(as[t * (LC + 1) + j], vs[j * dv + c], o);
+    out[(size_t)(t0 + t) * heads * dv + (size_t)head * dv + c] = o;
+  }
+  // what the chunk adds to the state
+  float* sum = sums + ((size_t)blockIdx.x * heads + head) * dk * dv;
+  for (int i = threadIdx.x; i < dk * dv; i += blockDim.x) {
+    const int r = i / dv, c = i - r * dv;
+    float s = 0.f;
+    for (int j = 0; j < len; ++j) s = fmaf(pw[len - 1 - j] * ks[j * (dk + 1) + r], vs[j * dv + c], s);
+    sum[i] = s;
+  }
+}
+
+__global__ void lr_chunk_scan_kernel(float* __restrict__ state, const int* __restrict__ slots,
+                                     const int* __restrict__ cu_tokens, const float* __restrict__ decay,
+                                     float* __restrict__ sums, int heads, int dk, int dv, int state_rows) {
+  pdl_trigger();
+  pdl_wait();
+  const int entry = blockIdx.x, head = blockIdx.y;
+  const int i = blockIdx.z * blockDim.x + threadIdx.x;
+  if (i >= dk * dv) return;
+  const int slot = slots[entry];
+  const int count = cu_tokens[entry + 1] - cu_tokens[entry];
+  if (slot < 0 || slot >= state_rows || count <= 0) return;
+  int first = 0;
+  for (int e = 0; e < entry; ++e) first += (cu_tokens[e + 1] - cu_tokens[e] + LC - 1) / LC;
+  const int chunks = (count + LC - 1) / LC;
+  const double lam = (double)decay[head];
+  float* cell = state + ((size_t)slot * heads + head) * dk * dv + i;
+  float s = *cell;
+  for (int c = 0; c < chunks; ++c) {
+    float* sum = sums + ((size_t)(first + c) * heads + head) * dk * dv + i;
+    const int len = min(LC, count - c * LC);
+    const float add = *sum;
+    *sum = s;                                            // the state this chunk starts from
+    s = fmaf((float)pow(lam, (double)len), s, add);
+  }
+  *cell = s;
+}
+
+template <typename TI>
+__global__ void __launch_bounds__(256)
+lr_chunk_state_kernel(const TI* __restrict__ proj, int ld, int q_off, int act, const int* __restrict__ cu_tokens,
+                      int entries, const float* __restrict__ decay, float* __restrict__ out,
+                      const float* __restrict__ sums, int heads, int dk, int dv) {
+  extern __shared__ float smem[];
+  float* qs = smem;                       // [LC][dk + 1]
+  float* ss = qs + LC * (dk + 1);         // [dk][dv]
+  float* pw = ss + dk * dv;               // [LC + 1]
+  pdl_trigger();
+  pdl_wait();
+  int entry, local, first;
+  if (!lr_locate(cu_tokens, entries, blockIdx.x, &entry, &local, &first)) return;
+  const int head = blockIdx.y;
+  const int t0 = cu_tokens[entry] + local * LC;
+  const int len = min(LC, cu_tokens[entry + 1] - t0);
+  const float lam = decay[head];
+  for (int i = threadIdx.x; i <= LC; i += blockDim.x) pw[i] = (float)pow((double)lam, (double)i);
+  for (int i = threadIdx.x; i < len * dk; i += blockDim.x) {
+    const int t = i / dk, d = i - t * dk;
+    qs[t * (dk + 1) + d] = lr_act(to_float(proj[(size_t)(t0 + t) * ld + q_off + (size_t)head * dk + d]), act);
+  }
+  const float* src = sums + ((size_t)blockIdx.x * heads + head) * dk * dv;
+  for (int i = threadIdx.x; i < dk * dv; i += blockDim.x) ss[i] = src[i];
+  __syncthreads();
+  for (int i = threadIdx.x; i < len * dv; i += blockDim.x) {
+    const int t = i / dv, c = i - t * dv;
+    const float* qt = qs + t * (dk + 1);
+    float o = 0.f;
+    for (int r = 0; r < dk; ++r) o = fmaf(qt[r], ss[r * dv + c], o);
+    float* dst = out + (size_t)(t0 + t) * heads * dv + (size_t)head * dv + c;
+    *dst = fmaf(pw[t + 1], o, *dst);
+  }
+}
+
+// Chunks of LC tokens a step of these sizes has at most, and floats of workspace per chunk.
+FE_EXPORT int fe_linear_recurrence_chunks(int n_tokens, int entries) { return (n_tokens + LC - 1) / LC + entries; }
+
+FE_EXPORT int fe_linear_recurrence_chunked(const void* proj, int dtype, int ld, int q_off, int k_off, int v_off, int act,
+                                           float* state, const int* slots, const int* cu_tokens, const float* decay,
+                                           float* out, float* sums, int n_tokens, int entries, int heads, int dk, int dv,
+                                           int state_rows, cudaStream_t stream) {
+  if (entries <= 0 || n_tokens <= 0) return 0;
+  if (dk < 1 || dv < 1 || heads > 65535 || entries > 65535) return FE_ERR_BAD_SHAPE;
+  const int chunks = fe_linear_recurrence_chunks(n_tokens, entries);
+  const size_t smem1 = sizeof(float) * ((size_t)2 * LC * (dk + 1) + (size_t)LC * dv + LC * (LC + 1) + LC + 1);
+  const size_t smem3 = sizeof(float) * ((size_t)LC * (dk + 1) + (size_t)dk * dv + LC + 1);
+  if (smem1 > 200 * 1024 || smem3 > 200 * 1024) return FE_ERR_TOO_LARGE;
+  int rc = 0;
+#define CHUNKED(TI)                                                                                                   \
+  do {                                                                                                                \
+    cudaFuncSetAttribute(lr_chunk_local_kernel<TI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);        \
+    cudaFuncSetAttribute(lr_chunk_state_kernel<TI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem3);        \
+    rc = fe_launch_dependent(lr_chunk_local_kernel<TI>, dim3(chunks, heads), dim3(256), smem1, stream,               \
+                             (const TI*)proj, ld, q_off, k_off, v_off, act, cu_tokens, entries, decay, out, sums,     \
+                             heads, dk, dv);                                                                          \
+    if (rc == 0)                                                                                                      \
+      rc = fe_launch_dependent(lr_chunk_scan_kernel, dim3(entries, heads, (dk * dv + 255) / 256), dim3(256), 0,      \
+                               stream, state, slots, cu_tokens, decay, sums, heads, dk, dv, state_rows);             \
+    if (rc == 0)                                                                                                      \
+      rc = fe_launch_dependent(lr_chunk_state_kernel<TI>, dim3(chunks, heads), dim3(256), smem3, stream,             \
+                               (const TI*)proj, ld, q_off, act, cu_tokens, entries, decay, out, sums, heads, dk, dv); \
+  } while (0)
+  if (dtype == FE_DTYPE_F32) CHUNKED(float);
+  else if (dtype == FE_DTYPE_BF16) CHUNKED(bf16);
+  else return FE_ERR_BAD_DTYPE;
+#undef CHUNKED
+  return rc ? rc : fe_last_error();
+}

@@ -64,6 +64,8 @@ def _declare(handle: ctypes.CDLL) -> None:
                            p, p, i, p, i, i, i, p, p, i, p, p],
         "fe_attention_general": [p, ll, ll, p, i, i, p, i, i, p, ll, ll, i, p, i, i, i, i, i, p, p, p, i, f, i, p, p],
         "fe_linear_recurrence": [p, i, i, i, i, i, i, p, p, p, p, p, i, i, i, i, i, p],
+        "fe_linear_recurrence_chunked": [p, i, i, i, i, i, i, p, p, p, p, p, p, i, i, i, i, i, i, p],
+        "fe_linear_recurrence_chunks": [i, i],
         "fe_gemm_simt_batched": [p, i, p, i, p, i, i, i, i, i, ll, ll, ll, ll, ll, p],
         "fe_add_rmsnorm": [p, p, i, p, p, i, p, i, i, f, i, p],
         "fe_silu_mul": [p, p, i, i, i, i, p],
@@ -513,6 +515,9 @@ def attention_general(
     )
 
 
+RECURRENCE_SERIAL_TOKENS = 16    # up to here an entry's tokens are walked one by one
+
+
 def linear_recurrence(
     proj: torch.Tensor,
     q_off: int,
@@ -525,16 +530,34 @@ def linear_recurrence(
     decay: torch.Tensor,
     out: torch.Tensor,
     entries: int,
+    max_new: int = 1,
 ) -> None:
     """S = decay_h S + k v^T, o = S^T q token by token for every entry of the step, from and
     to the 32-bit ``state`` [slots, heads, dk, dv] rows named by ``slots``.  q, k, v are
     act(columns of ``proj``) starting at ``q_off``, ``k_off`` (heads x dk each) and ``v_off``
-    (heads x dv); ``act`` ACT_SILU or -1 for none.  ``out`` 32-bit [N, heads * dv]."""
+    (heads x dv); ``act`` ACT_SILU or -1 for none.  ``out`` 32-bit [N, heads * dv].
+    ``max_new``: the most tokens an entry brings; beyond RECURRENCE_SERIAL_TOKENS the step
+    runs chunk-parallel (chunks of 64 tokens side by side, their states chained afterwards)
+    where the chunk kernels' tiles fit shared memory."""
     _dense(proj, "proj"), _dense(state, "state"), _dense(out, "out")
     rows, heads, dk, dv = state.shape
     assert state.dtype == torch.float32 and out.dtype == torch.float32 and decay.dtype == torch.float32
     assert decay.numel() == heads and out.shape == (proj.shape[0], heads * dv)
     assert slots.dtype == torch.int32 and cu_tokens.dtype == torch.int32
+    n = proj.shape[0]
+    fits = 4 * max(2 * 64 * (dk + 1) + 64 * dv + 64 * 65 + 65, 64 * (dk + 1) + dk * dv + 65) <= 200 * 1024
+    if max_new > RECURRENCE_SERIAL_TOKENS and fits:
+        chunks = int(lib().fe_linear_recurrence_chunks(int(n), int(entries)))
+        sums = _scratch.get("recurrence chunk states", proj.device, chunks * heads * dk * dv, torch.float32, 1 << 22)
+        check(
+            lib().fe_linear_recurrence_chunked(ptr(proj), code(proj), int(proj.shape[1]), int(q_off), int(k_off),
+                                               int(v_off), int(act), ptr(state), ptr(slots), ptr(cu_tokens), ptr(decay),
+                                               ptr(out), ptr(sums), int(n), int(entries), heads, dk, dv, rows, stream()),
+            "linear_recurrence (chunked)",
+        )
+        global LAUNCHES
+        LAUNCHES += 2
+        return
     check(
         lib().fe_linear_recurrence(ptr(proj), code(proj), int(proj.shape[1]), int(q_off), int(k_off), int(v_off),
                                    int(act), ptr(state), ptr(slots), ptr(cu_tokens), ptr(decay), ptr(out),

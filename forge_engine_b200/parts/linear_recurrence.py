@@ -64,7 +64,7 @@ class LinearRecurrence(Mixer):
         mixed = torch.empty((n, v), dtype=torch.float32, device=x.device)
         with self.ctx.section("mixer.recurrence"):
             native.linear_recurrence(proj, 0, qk, 2 * qk, self.act, cache.state, batch.slots, batch.cu_tokens,
-                                     self.decay, mixed, batch.n_entries)
+                                     self.decay, mixed, batch.n_entries, batch.max_new)
         gated = torch.empty((n, v), dtype=self.ctx.dtype, device=x.device)
         with self.ctx.section("mixer.gate_norm"):
             native.gated_rmsnorm(mixed, proj[:, 2 * qk + v:], self.norm, gated, self.spec.norm_eps)

@@ -431,7 +431,8 @@ def test_recurrence_state_is_carried_in_32_bit(tmp_path):
             state = decay[h] * state + torch.outer(kt, vt)
             want[t, h] = state.T @ act[t, h * dk : (h + 1) * dk]
     device = "cuda"
-    for cuts in ([T], [1] * 40 + [T - 40], [7, 2, 100, 1, 1, 189]):
+    # portions of up to 16 tokens are walked token by token, longer ones chunk-parallel
+    for cuts in ([T], [1] * 40 + [T - 40], [7, 2, 100, 1, 1, 189], [16] * 18 + [12], [65, 64, 63, 108]):
         state = torch.zeros(3, H, dk, dv, dtype=torch.float32, device=device)
         out = torch.empty(T, H * dv, dtype=torch.float32, device=device)
         begin = 0
@@ -441,7 +442,7 @@ def test_recurrence_state_is_carried_in_32_bit(tmp_path):
             native.linear_recurrence(piece, 0, H * dk, 2 * H * dk, native.ACT_SILU, state,
                                      torch.tensor([1], dtype=torch.int32, device=device),
                                      torch.tensor([0, count], dtype=torch.int32, device=device),
-                                     torch.tensor(decay, dtype=torch.float32, device=device), part, 1)
+                                     torch.tensor(decay, dtype=torch.float32, device=device), part, 1, count)
             out[begin : begin + count] = part
             begin += count
         assert float(state[0].abs().max()) == 0 and float(state[2].abs().max()) == 0
