@@ -26,6 +26,7 @@ namespace {
 constexpr int DK = FE_DK, DV = FE_DV;
 constexpr bool V_IN_K = FE_V_IN_K != 0;
 constexpr int BM = 64, WARPS = 4;
+constexpr float LOG2E = 1.4426950408889634f;
 constexpr int BN = DK > 320 ? 32 : 64;
 constexpr int KS = DK + 8;                     // row stride of the Q and K tiles in shared memory
 constexpr int VS = DV + 8;
@@ -115,42 +116,28 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(Params p, 
   const int per = (kt_hi - kt_lo + p.splits - 1) / p.splits;
   const int my_lo = kt_lo + split * per, my_hi = min(kt_hi, my_lo + per);
 
+  // TPR threads fetch one key row: its page is looked up once per row and tile
+  constexpr int TPR = WARPS * 32 / BN;
+  const int load_row = tid / TPR, load_piece = tid % TPR;
   auto load_tile = [&](int kt, int stage) {
-    bf16* kd = Ks + stage * K_TILE;
-    for (int idx = tid; idx < BN * QC; idx += WARPS * 32) {
-      const int r = idx / QC, c = idx - r * QC;
-      const int key = kt * BN + r;
-      bool valid = key >= key_lo && key <= key_hi;
-      const bf16* src = p.k;
-      if (valid) {
-        const int logical = key / p.page_size;
-        const int page = logical < p.max_pages ? table[logical] : -1;
-        if (page < 0 || page >= p.num_pages) {
-          valid = false;                     // a page the window has given back: its keys are masked anyway
-        } else {
-          src = p.k + (((size_t)page * p.nkv + kvh) * p.page_size + (key - logical * p.page_size)) * p.k_row + c * 8;
-        }
-      }
-      cp_async16(kd + r * KS + c * 8, src, valid);
+    const int key = kt * BN + load_row;
+    bool valid = key >= key_lo && key <= key_hi;
+    size_t row = 0;
+    if (valid) {
+      const int logical = key / p.page_size;
+      const int page = logical < p.max_pages ? table[logical] : -1;
+      if (page < 0 || page >= p.num_pages) valid = false;     // a page the window has given back: its keys are masked anyway
+      else row = ((size_t)page * p.nkv + kvh) * p.page_size + (key - logical * p.page_size);
     }
+    const bf16* ksrc = p.k + row * p.k_row;
+    bf16* kd = Ks + stage * K_TILE + load_row * KS;
+#pragma unroll
+    for (int c = load_piece; c < QC; c += TPR) cp_async16(kd + c * 8, ksrc + c * 8, valid);
     if constexpr (!V_IN_K) {
-      bf16* vd = Vs + stage * V_TILE;
-      for (int idx = tid; idx < BN * VC; idx += WARPS * 32) {
-        const int r = idx / VC, c = idx - r * VC;
-        const int key = kt * BN + r;
-        bool valid = key >= key_lo && key <= key_hi;
-        const bf16* src = p.v;
-        if (valid) {
-          const int logical = key / p.page_size;
-          const int page = logical < p.max_pages ? table[logical] : -1;
-          if (page < 0 || page >= p.num_pages) {
-            valid = false;
-          } else {
-            src = p.v + (((size_t)page * p.nkv + kvh) * p.page_size + (key - logical * p.page_size)) * p.v_row + c * 8;
-          }
-        }
-        cp_async16(vd + r * VS + c * 8, src, valid);
-      }
+      const bf16* vsrc = p.v + row * p.v_row;
+      bf16* vd = Vs + stage * V_TILE + load_row * VS;
+#pragma unroll
+      for (int c = load_piece; c < VC; c += TPR) cp_async16(vd + c * 8, vsrc + c * 8, valid);
     }
   };
 
@@ -164,8 +151,13 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(Params p, 
     const int rho = row0 + warp * 16 + quad + 8 * h;
     row_live[h] = rho < rows_total;
     row_pos[h] = row_live[h] ? start + rho / p.groups : -1;
-    row_slope[h] = (row_live[h] && p.slopes) ? p.slopes[kvh * p.groups + rho % p.groups] : 0.f;
+    row_slope[h] = (row_live[h] && p.slopes) ? p.slopes[kvh * p.groups + rho % p.groups] * LOG2E : 0.f;
   }
+  const float scale2 = p.scale * LOG2E;       // scores are kept in units of log 2, so that exp is one exp2
+  // rows of this warp, first and last position (all sixteen live), for tiles that need no mask
+  const bool warp_full = row0 + warp * 16 + 15 < rows_total;
+  const int warp_pos_lo = start + (row0 + warp * 16) / p.groups, warp_pos_hi = start + (row0 + warp * 16 + 15) / p.groups;
+  const bool warp_live = row0 + warp * 16 < rows_total;
   float o[DV / 8][4];
 #pragma unroll
   for (int n = 0; n < DV / 8; ++n)
@@ -190,6 +182,10 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(Params p, 
     const bf16* kd = Ks + stage * K_TILE;
     const bf16* vd = V_IN_K ? kd : Vs + stage * V_TILE;
     constexpr int vstride = V_IN_K ? KS : VS;
+    if (!warp_live) {            // a warp whose sixteen rows lie past the entry's last row only loads
+      __syncthreads();
+      continue;
+    }
 
     float s[BN / 8][4];
 #pragma unroll
@@ -211,16 +207,32 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(Params p, 
 
     // scale, bias, mask; running maximum and normaliser
     float mx[2] = {-INFINITY, -INFINITY};
+    // every key of the tile is visible to every row of the warp: no comparisons
+    const bool inside = warp_full && kt * BN + BN - 1 <= warp_pos_lo && (p.window <= 0 || kt * BN > warp_pos_hi - p.window);
+    if (inside) {
 #pragma unroll
-    for (int j = 0; j < BN / 8; ++j) {
+      for (int j = 0; j < BN / 8; ++j) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const int h = c >> 1;
-        const int key = kt * BN + j * 8 + pair * 2 + (c & 1);
-        const bool visible = row_live[h] && key <= row_pos[h] && (p.window <= 0 || key > row_pos[h] - p.window);
-        const float sc = visible ? s[j][c] * p.scale - row_slope[h] * (float)(row_pos[h] - key) : -INFINITY;
-        s[j][c] = sc;
-        mx[h] = fmaxf(mx[h], sc);
+        for (int c = 0; c < 4; ++c) {
+          const int h = c >> 1;
+          const int key = kt * BN + j * 8 + pair * 2 + (c & 1);
+          const float sc = s[j][c] * scale2 - row_slope[h] * (float)(row_pos[h] - key);
+          s[j][c] = sc;
+          mx[h] = fmaxf(mx[h], sc);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < BN / 8; ++j) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int h = c >> 1;
+          const int key = kt * BN + j * 8 + pair * 2 + (c & 1);
+          const bool visible = row_live[h] && key <= row_pos[h] && (p.window <= 0 || key > row_pos[h] - p.window);
+          const float sc = visible ? s[j][c] * scale2 - row_slope[h] * (float)(row_pos[h] - key) : -INFINITY;
+          s[j][c] = sc;
+          mx[h] = fmaxf(mx[h], sc);
+        }
       }
     }
     float corr[2], base[2];
@@ -230,7 +242,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(Params p, 
       mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
       const float m_new = fmaxf(m_run[h], mx[h]);
       base[h] = m_new == -INFINITY ? 0.f : m_new;
-      corr[h] = expf(m_run[h] - base[h]);
+      corr[h] = exp2f(m_run[h] - base[h]);
       m_run[h] = m_new;
       l_run[h] *= corr[h];
     }
@@ -238,7 +250,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(Params p, 
     for (int j = 0; j < BN / 8; ++j) {
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        const float w = expf(s[j][c] - base[c >> 1]);
+        const float w = exp2f(s[j][c] - base[c >> 1]);
         s[j][c] = w;
         l_run[c >> 1] += w;
       }
@@ -308,30 +320,45 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(Params p, 
   }
 }
 
+constexpr int MERGE_ROWS = 4, MAX_SPLITS = 32;
+
+// A block combines MERGE_ROWS rows of one row tile: the splits' weights once per row (in a
+// fixed order), then every value column.
 __global__ void __launch_bounds__(128) attention_mma_merge_kernel(Params p) {
+  __shared__ float weight[MERGE_ROWS][MAX_SPLITS];
+  __shared__ float inverse[MERGE_ROWS];
   pdl_trigger();
   pdl_wait();
-  const int tile = blockIdx.x, entry = blockIdx.y, kvh = blockIdx.z;
+  const int tile = blockIdx.x / (BM / MERGE_ROWS), piece = blockIdx.x % (BM / MERGE_ROWS);
+  const int entry = blockIdx.y, kvh = blockIdx.z;
   const int t_begin = p.cu_tokens[entry];
   const int rows_total = (p.cu_tokens[entry + 1] - t_begin) * p.groups;
-  const int row0 = tile * BM;
-  if (row0 >= rows_total) return;
+  const int first = tile * BM + piece * MERGE_ROWS;
+  if (first >= rows_total) return;
   const float* base = p.part + (((size_t)entry * p.tiles + tile) * p.nkv + kvh) * p.splits * (size_t)BM * (DV + 2);
-  const int rows = min(BM, rows_total - row0);
-  for (int idx = threadIdx.x; idx < rows * DV; idx += blockDim.x) {
-    const int r = idx / DV, d = idx - r * DV;
+  const int rows = min(MERGE_ROWS, rows_total - first);
+  if (threadIdx.x < rows) {
+    const int r = piece * MERGE_ROWS + threadIdx.x;
     float big = -INFINITY;
     for (int s = 0; s < p.splits; ++s) big = fmaxf(big, base[((size_t)s * BM + r) * (DV + 2) + DV]);
-    float num = 0.f, den = 0.f;
+    float den = 0.f;
     for (int s = 0; s < p.splits; ++s) {
       const float* row = base + ((size_t)s * BM + r) * (DV + 2);
-      const float f = row[DV] == -INFINITY ? 0.f : expf(row[DV] - big);
-      num = fmaf(row[d], f, num);
+      const float f = row[DV] == -INFINITY ? 0.f : exp2f(row[DV] - big);      // maxima are in units of log 2
+      weight[threadIdx.x][s] = f;
       den = fmaf(row[DV + 1], f, den);
     }
-    const int rho = row0 + r;
+    inverse[threadIdx.x] = den > 0.f ? 1.f / den : 0.f;
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < rows * DV; idx += blockDim.x) {
+    const int lr = idx / DV, d = idx - lr * DV;
+    const int r = piece * MERGE_ROWS + lr;
+    float num = 0.f;
+    for (int s = 0; s < p.splits; ++s) num = fmaf(base[((size_t)s * BM + r) * (DV + 2) + d], weight[lr][s], num);
+    const int rho = tile * BM + r;
     const int token = t_begin + rho / p.groups, head = kvh * p.groups + rho % p.groups;
-    p.out[(size_t)token * p.o_ts + (size_t)head * p.o_hs + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+    p.out[(size_t)token * p.o_ts + (size_t)head * p.o_hs + d] = __float2bfloat16_rn(num * inverse[lr]);
   }
 }
 
@@ -355,6 +382,7 @@ FE_EXPORT int GM_NAME(fe_attention_gmma_)(const void* q, long long q_ts, long lo
   if (k_row % 8 || v_row % 8 || q_ts % 8 || q_hs % 8 || o_ts % 2 || o_hs % 2) return FE_ERR_BAD_ALIGN;
   if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) % 16 || (uintptr_t)out % 4) return FE_ERR_BAD_ALIGN;
   if (splits < 1) splits = 1;
+  if (splits > MAX_SPLITS) return FE_ERR_BAD_SHAPE;
   if (splits > 1 && workspace == nullptr) return FE_ERR_BAD_SHAPE;
   const int groups = num_q_heads / nkv;
   const int tiles = (int)(((long long)max_new * groups + BM - 1) / BM);
@@ -371,7 +399,7 @@ FE_EXPORT int GM_NAME(fe_attention_gmma_)(const void* q, long long q_ts, long lo
   int rc = fe_launch_dependent(attention_mma_kernel, grid, dim3(WARPS * 32), SMEM_BYTES, stream, p, status);
   if (rc) return rc;
   if (splits > 1) {
-    rc = fe_launch_dependent(attention_mma_merge_kernel, dim3(tiles, entries, nkv), dim3(128), 0, stream, p);
+    rc = fe_launch_dependent(attention_mma_merge_kernel, dim3(tiles * (BM / MERGE_ROWS), entries, nkv), dim3(128), 0, stream, p);
     if (rc) return rc;
   }
   return fe_last_error();

@@ -90,6 +90,101 @@ stream_mix_norm_kernel(float* __restrict__ streams, int S, const TU* __restrict_
   for (int i = threadIdx.x; i < W; i += blockDim.x) dst[i] = from_float<TO>((u_row[i] - mean) * inv * weight[i]);
 }
 
+// The same for widths that are multiples of 4 (and 16-byte aligned rows): a thread handles four
+// neighbouring elements of every stream with 16-byte loads and stores; same arithmetic, same
+// order of sums.
+template <typename TU, typename TO>
+__global__ void __launch_bounds__(256)
+stream_mix_norm_vec_kernel(float* __restrict__ streams, int S, const TU* __restrict__ update, float update_scale,
+                           const float* __restrict__ mix, const float* __restrict__ out_coef,
+                           const float* __restrict__ in_coef, int norm_kind, const float* __restrict__ weight,
+                           float eps, TO* __restrict__ out, const int* __restrict__ row_map, int W,
+                           int write_streams) {
+  extern __shared__ float u_row[];          // [W]
+  __shared__ float scratch[33];
+  __shared__ float c_mix[FE_MAX_STREAMS * FE_MAX_STREAMS], c_out[FE_MAX_STREAMS], c_in[FE_MAX_STREAMS];
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const int src = row_map ? row_map[r] : r;
+  if (threadIdx.x < S * S) c_mix[threadIdx.x] = mix ? mix[threadIdx.x] : ((threadIdx.x / S) == (threadIdx.x % S) ? 1.f : 0.f);
+  if (threadIdx.x < S) {
+    c_out[threadIdx.x] = (out_coef ? out_coef[threadIdx.x] : 1.f) * update_scale;
+    c_in[threadIdx.x] = in_coef ? in_coef[threadIdx.x] : 1.f;
+  }
+  __syncthreads();
+  float* base = streams + (size_t)src * S * W;
+  const TU* upd = update ? update + (size_t)src * W : nullptr;
+  float total = 0.f;
+  for (int i = threadIdx.x * 4; i < W; i += blockDim.x * 4) {
+    float x[FE_MAX_STREAMS][4];
+#pragma unroll
+    for (int s = 0; s < FE_MAX_STREAMS; ++s)
+      if (s < S) load4(base + (size_t)s * W + i, x[s]);
+    float u[4] = {0.f, 0.f, 0.f, 0.f};
+    if (upd) {
+      float y[4];
+      load4(upd + i, y);
+#pragma unroll
+      for (int t = 0; t < FE_MAX_STREAMS; ++t) {
+        if (t < S) {
+          float v[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int s = 0; s < FE_MAX_STREAMS; ++s)
+            if (s < S) {
+#pragma unroll
+              for (int e = 0; e < 4; ++e) v[e] = fmaf(c_mix[s * S + t], x[s][e], v[e]);
+            }
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            v[e] = fmaf(c_out[t], y[e], v[e]);
+            u[e] = fmaf(c_in[t], v[e], u[e]);
+          }
+          if (write_streams) store4(base + (size_t)t * W + i, v);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int t = 0; t < FE_MAX_STREAMS; ++t)
+        if (t < S) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) u[e] = fmaf(c_in[t], x[t][e], u[e]);
+        }
+    }
+    store4(u_row + i, u);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) total += norm_kind == FE_NORM_RMS ? u[e] * u[e] : u[e];
+  }
+  if (out == nullptr) return;
+  float mean = 0.f, inv = 1.f;
+  if (norm_kind != FE_NORM_NONE) {
+    total = block_sum(total, scratch);
+    if (norm_kind == FE_NORM_RMS) {
+      inv = 1.f / sqrtf(total / (float)W + eps);
+    } else {
+      mean = total / (float)W;
+      float dev = 0.f;
+      for (int i = threadIdx.x * 4; i < W; i += blockDim.x * 4) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float d = u_row[i + e] - mean;
+          dev = fmaf(d, d, dev);
+        }
+      }
+      dev = block_sum(dev, scratch);
+      inv = 1.f / sqrtf(dev / (float)W + eps);
+    }
+  }
+  TO* dst = out + (size_t)r * W;
+  for (int i = threadIdx.x * 4; i < W; i += blockDim.x * 4) {
+    float y[4], w[4] = {1.f, 1.f, 1.f, 1.f};
+    if (norm_kind != FE_NORM_NONE) load4(weight + i, w);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) y[e] = norm_kind == FE_NORM_NONE ? u_row[i + e] : (u_row[i + e] - mean) * inv * w[e];
+    store4(dst + i, y);
+  }
+}
+
 FE_EXPORT int fe_stream_mix_norm(float* streams, int n_streams, const void* update, int update_dtype,
                                  float update_scale, const float* mix, const float* out_coef, const float* in_coef,
                                  int norm_kind, const float* weight, float eps, void* out, int out_dtype,
@@ -99,13 +194,18 @@ FE_EXPORT int fe_stream_mix_norm(float* streams, int n_streams, const void* upda
   if (norm_kind != FE_NORM_NONE && out != nullptr && weight == nullptr) return FE_ERR_BAD_SHAPE;
   const size_t smem = sizeof(float) * (size_t)width;
   if (smem > 200 * 1024) return FE_ERR_TOO_LARGE;
-  const int threads = width >= 2048 ? 256 : 128;
+  int threads = width >= 2048 ? 256 : 128;
   int rc = 0;
+  const int update_bytes = update_dtype == FE_DTYPE_F32 ? 16 : 8, out_bytes = out_dtype == FE_DTYPE_F32 ? 16 : 8;
+  const bool vec = (width % 4) == 0 && ((uintptr_t)streams % 16) == 0 && ((uintptr_t)weight % 16) == 0 &&
+                   ((uintptr_t)update % update_bytes) == 0 && ((uintptr_t)out % out_bytes) == 0;
+  if (vec) threads = width >= 1024 ? 256 : width >= 512 ? 128 : 64;
 #define LAUNCH(TU, TO)                                                                                          \
   do {                                                                                                          \
+    auto kernel = vec ? stream_mix_norm_vec_kernel<TU, TO> : stream_mix_norm_kernel<TU, TO>;                    \
     if (smem > 48 * 1024)                                                                                       \
-      cudaFuncSetAttribute(stream_mix_norm_kernel<TU, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    rc = fe_launch_dependent(stream_mix_norm_kernel<TU, TO>, dim3(rows), dim3(threads), smem, stream, streams,  \
+      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                     \
+    rc = fe_launch_dependent(kernel, dim3(rows), dim3(threads), smem, stream, streams,                          \
                              n_streams, (const TU*)update, update_scale, mix, out_coef, in_coef, norm_kind,     \
                              weight, eps, (TO*)out, row_map, width, write_streams);                             \
   } while (0)
@@ -139,11 +239,40 @@ __global__ void act_mul_kernel(const TI* __restrict__ gate_up, TO* __restrict__ 
     o[i] = from_float<TO>(act_apply(to_float(g[i]), act) * to_float(g[inter + i]));
 }
 
+template <typename TI, typename TO>
+__global__ void act_mul_vec_kernel(const TI* __restrict__ gate_up, TO* __restrict__ out, int inter, int act) {
+  pdl_trigger();
+  pdl_wait();
+  const int row = blockIdx.x;
+  const TI* g = gate_up + (size_t)row * 2 * inter;
+  TO* o = out + (size_t)row * inter;
+  for (int i = (blockIdx.y * blockDim.x + threadIdx.x) * 4; i < inter; i += gridDim.y * blockDim.x * 4) {
+    float a[4], b[4];
+    load4(g + i, a);
+    load4(g + inter + i, b);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) a[e] = act_apply(a[e], act) * b[e];
+    store4(o + i, a);
+  }
+}
+
 FE_EXPORT int fe_act_mul(const void* gate_up, int in_dtype, void* out, int out_dtype, int rows, int inter, int act,
                          cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (act != 0 && act != 1) return FE_ERR_BAD_SHAPE;
   const int threads = 256;
+  if ((inter % 4) == 0 && ((uintptr_t)gate_up % 16) == 0 && ((uintptr_t)out % 16) == 0) {
+    int pieces = (inter / 4 + threads - 1) / threads;
+    if (pieces > 64) pieces = 64;
+    dim3 vgrid(rows, pieces);
+    if (in_dtype == FE_DTYPE_F32 && out_dtype == FE_DTYPE_F32)
+      return fe_launch_dependent(act_mul_vec_kernel<float, float>, vgrid, dim3(threads), 0, stream, (const float*)gate_up, (float*)out, inter, act);
+    if (in_dtype == FE_DTYPE_BF16 && out_dtype == FE_DTYPE_BF16)
+      return fe_launch_dependent(act_mul_vec_kernel<bf16, bf16>, vgrid, dim3(threads), 0, stream, (const bf16*)gate_up, (bf16*)out, inter, act);
+    if (in_dtype == FE_DTYPE_F32 && out_dtype == FE_DTYPE_BF16)
+      return fe_launch_dependent(act_mul_vec_kernel<float, bf16>, vgrid, dim3(threads), 0, stream, (const float*)gate_up, (bf16*)out, inter, act);
+    return FE_ERR_BAD_DTYPE;
+  }
   int chunks = (inter + threads - 1) / threads;
   if (chunks > 64) chunks = 64;
   dim3 grid(rows, chunks);
