@@ -157,17 +157,30 @@ __device__ __forceinline__ bool lr_locate(const int* cu_tokens, int entries, int
   return false;
 }
 
+// Shared-memory layout of the chunk kernels: q row-major [LC][dk]; k transposed [dk][LCP], so
+// that four neighbouring keys are one 16-byte load; v [LC][dv] and the state [dk][dv] with four
+// neighbouring columns per load.  A thread owns two rows (32 apart) and four columns of an
+// output tile: 8 multiply-adds per three loads.  dv is a multiple of 4.
+#define LCP (LC + 4)
+
+__device__ __forceinline__ void fma4(float* acc, float a, const float4& b) {
+  acc[0] = fmaf(a, b.x, acc[0]);
+  acc[1] = fmaf(a, b.y, acc[1]);
+  acc[2] = fmaf(a, b.z, acc[2]);
+  acc[3] = fmaf(a, b.w, acc[3]);
+}
+
 template <typename TI>
 __global__ void __launch_bounds__(256)
 lr_chunk_local_kernel(const TI* __restrict__ proj, int ld, int q_off, int k_off, int v_off, int act,
                       const int* __restrict__ cu_tokens, int entries, const float* __restrict__ decay,
                       float* __restrict__ out, float* __restrict__ sums, int heads, int dk, int dv) {
-  extern __shared__ float smem[];
-  float* qs = smem;                       // [LC][dk + 1]
-  float* ks = qs + LC * (dk + 1);         // [LC][dk + 1]
-  float* vs = ks + LC * (dk + 1);         // [LC][dv]
-  float* as = vs + LC * dv;               // [LC][LC + 1]
-  float* pw = as + LC * (LC + 1);         // [LC + 1] powers of the decay
+  extern __shared__ __align__(16) float smem[];
+  float* qs = smem;                       // [LC][dk]
+  float* kt = qs + LC * dk;               // [dk][LCP]
+  float* vs = kt + dk * LCP;              // [LC][dv]
+  float* as = vs + LC * dv;               // [LC][LCP]
+  float* pw = as + LC * LCP;              // [LC + 1] powers of the decay
   pdl_trigger();
   pdl_wait();
   int entry, local, first;
@@ -177,43 +190,74 @@ lr_chunk_local_kernel(const TI* __restrict__ proj, int ld, int q_off, int k_off,
   const int len = min(LC, cu_tokens[entry + 1] - t0);
   const float lam = decay[head];
   for (int i = threadIdx.x; i <= LC; i += blockDim.x) pw[i] = (float)pow((double)lam, (double)i);
-  for (int i = threadIdx.x; i < len * dk; i += blockDim.x) {
+  for (int i = threadIdx.x; i < LC * dk; i += blockDim.x) {
     const int t = i / dk, d = i - t * dk;
-    const TI* row = proj + (size_t)(t0 + t) * ld + (size_t)head * dk + d;
-    qs[t * (dk + 1) + d] = lr_act(to_float(row[q_off]), act);
-    ks[t * (dk + 1) + d] = lr_act(to_float(row[k_off]), act);
-  }
-  for (int i = threadIdx.x; i < len * dv; i += blockDim.x) {
-    const int t = i / dv, c = i - t * dv;
-    vs[i] = lr_act(to_float(proj[(size_t)(t0 + t) * ld + v_off + (size_t)head * dv + c]), act);
-  }
-  __syncthreads();
-  // weights of the chunk's own keys
-  for (int i = threadIdx.x; i < len * LC; i += blockDim.x) {
-    const int t = i / LC, j = i - t * LC;
-    float w = 0.f;
-    if (j <= t) {
-      const float* qt = qs + t * (dk + 1);
-      const float* kj = ks + j * (dk + 1);
-      for (int d = 0; d < dk; ++d) w = fmaf(qt[d], kj[d], w);
-      w *= pw[t - j];
+    float q = 0.f, k = 0.f;
+    if (t < len) {
+      const TI* row = proj + (size_t)(t0 + t) * ld + (size_t)head * dk + d;
+      q = lr_act(to_float(row[q_off]), act);
+      k = lr_act(to_float(row[k_off]), act);
     }
-    as[t * (LC + 1) + j] = w;
+    qs[i] = q;
+    kt[d * LCP + t] = k;
+  }
+  for (int i = threadIdx.x; i < LC * dv; i += blockDim.x) {
+    const int t = i / dv, c = i - t * dv;
+    vs[i] = t < len ? lr_act(to_float(proj[(size_t)(t0 + t) * ld + v_off + (size_t)head * dv + c]), act) : 0.f;
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < len * dv; i += blockDim.x) {
-    const int t = i / dv, c = i - t * dv;
-    float o = 0.f;
-    for (int j = 0; j <= t; ++j) o = fmaf(as[t * (LC + 1) + j], vs[j * dv + c], o);
-    out[(size_t)(t0 + t) * heads * dv + (size_t)head * dv + c] = o;
+  // weights of the chunk's own keys: as[t][j] = decay^(t - j) q_t . k_j for j <= t, else 0
+  for (int item = threadIdx.x; item < 32 * (LC / 4); item += blockDim.x) {
+    const int tp = item / (LC / 4), j4 = (item - tp * (LC / 4)) * 4;
+    const int t1 = tp, t2 = tp + 32;
+    float a1[4] = {0.f, 0.f, 0.f, 0.f}, a2[4] = {0.f, 0.f, 0.f, 0.f};
+    if (j4 <= t2) {
+      const float* q1 = qs + t1 * dk;
+      const float* q2 = qs + t2 * dk;
+      for (int d = 0; d < dk; ++d) {
+        const float4 k4 = *reinterpret_cast<const float4*>(kt + d * LCP + j4);
+        fma4(a1, q1[d], k4);
+        fma4(a2, q2[d], k4);
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int j = j4 + e;
+      as[t1 * LCP + j] = j <= t1 ? a1[e] * pw[t1 - j] : 0.f;
+      as[t2 * LCP + j] = j <= t2 ? a2[e] * pw[t2 - j] : 0.f;
+    }
   }
-  // what the chunk adds to the state
+  __syncthreads();
+  const int dv4 = dv >> 2;
+  for (int item = threadIdx.x; item < 32 * dv4; item += blockDim.x) {
+    const int tp = item / dv4, c = (item - tp * dv4) * 4;
+    const int t1 = tp, t2 = tp + 32;
+    float o1[4] = {0.f, 0.f, 0.f, 0.f}, o2[4] = {0.f, 0.f, 0.f, 0.f};
+    const int last = min(len, t2 + 1);
+    for (int j = 0; j < last; ++j) {
+      const float4 v4 = *reinterpret_cast<const float4*>(vs + j * dv + c);
+      fma4(o1, as[t1 * LCP + j], v4);
+      fma4(o2, as[t2 * LCP + j], v4);
+    }
+    if (t1 < len) store4(out + (size_t)(t0 + t1) * heads * dv + (size_t)head * dv + c, o1);
+    if (t2 < len) store4(out + (size_t)(t0 + t2) * heads * dv + (size_t)head * dv + c, o2);
+  }
+  // what the chunk adds to the state: sum_j decay^(len - 1 - j) k_j v_j^T
   float* sum = sums + ((size_t)blockIdx.x * heads + head) * dk * dv;
-  for (int i = threadIdx.x; i < dk * dv; i += blockDim.x) {
-    const int r = i / dv, c = i - r * dv;
-    float s = 0.f;
-    for (int j = 0; j < len; ++j) s = fmaf(pw[len - 1 - j] * ks[j * (dk + 1) + r], vs[j * dv + c], s);
-    sum[i] = s;
+  const int half = (dk + 1) >> 1;
+  for (int item = threadIdx.x; item < half * dv4; item += blockDim.x) {
+    const int rp = item / dv4, c = (item - rp * dv4) * 4;
+    const int r1 = rp, r2 = rp + half;
+    const bool second = r2 < dk;
+    float s1[4] = {0.f, 0.f, 0.f, 0.f}, s2[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < len; ++j) {
+      const float4 v4 = *reinterpret_cast<const float4*>(vs + j * dv + c);
+      const float w = pw[len - 1 - j];
+      fma4(s1, w * kt[r1 * LCP + j], v4);
+      if (second) fma4(s2, w * kt[r2 * LCP + j], v4);
+    }
+    store4(sum + (size_t)r1 * dv + c, s1);
+    if (second) store4(sum + (size_t)r2 * dv + c, s2);
   }
 }
 
@@ -249,9 +293,9 @@ __global__ void __launch_bounds__(256)
 lr_chunk_state_kernel(const TI* __restrict__ proj, int ld, int q_off, int act, const int* __restrict__ cu_tokens,
                       int entries, const float* __restrict__ decay, float* __restrict__ out,
                       const float* __restrict__ sums, int heads, int dk, int dv) {
-  extern __shared__ float smem[];
-  float* qs = smem;                       // [LC][dk + 1]
-  float* ss = qs + LC * (dk + 1);         // [dk][dv]
+  extern __shared__ __align__(16) float smem[];
+  float* qs = smem;                       // [LC][dk]
+  float* ss = qs + LC * dk;               // [dk][dv]
   float* pw = ss + dk * dv;               // [LC + 1]
   pdl_trigger();
   pdl_wait();
@@ -262,20 +306,40 @@ lr_chunk_state_kernel(const TI* __restrict__ proj, int ld, int q_off, int act, c
   const int len = min(LC, cu_tokens[entry + 1] - t0);
   const float lam = decay[head];
   for (int i = threadIdx.x; i <= LC; i += blockDim.x) pw[i] = (float)pow((double)lam, (double)i);
-  for (int i = threadIdx.x; i < len * dk; i += blockDim.x) {
+  for (int i = threadIdx.x; i < LC * dk; i += blockDim.x) {
     const int t = i / dk, d = i - t * dk;
-    qs[t * (dk + 1) + d] = lr_act(to_float(proj[(size_t)(t0 + t) * ld + q_off + (size_t)head * dk + d]), act);
+    qs[i] = t < len ? lr_act(to_float(proj[(size_t)(t0 + t) * ld + q_off + (size_t)head * dk + d]), act) : 0.f;
   }
   const float* src = sums + ((size_t)blockIdx.x * heads + head) * dk * dv;
-  for (int i = threadIdx.x; i < dk * dv; i += blockDim.x) ss[i] = src[i];
+  for (int i = threadIdx.x * 4; i < dk * dv; i += blockDim.x * 4)
+    *reinterpret_cast<float4*>(ss + i) = *reinterpret_cast<const float4*>(src + i);
   __syncthreads();
-  for (int i = threadIdx.x; i < len * dv; i += blockDim.x) {
-    const int t = i / dv, c = i - t * dv;
-    const float* qt = qs + t * (dk + 1);
-    float o = 0.f;
-    for (int r = 0; r < dk; ++r) o = fmaf(qt[r], ss[r * dv + c], o);
-    float* dst = out + (size_t)(t0 + t) * heads * dv + (size_t)head * dv + c;
-    *dst = fmaf(pw[t + 1], o, *dst);
+  const int dv4 = dv >> 2;
+  for (int item = threadIdx.x; item < 32 * dv4; item += blockDim.x) {
+    const int tp = item / dv4, c = (item - tp * dv4) * 4;
+    const int t1 = tp, t2 = tp + 32;
+    if (t1 >= len) continue;
+    float o1[4] = {0.f, 0.f, 0.f, 0.f}, o2[4] = {0.f, 0.f, 0.f, 0.f};
+    const float* q1 = qs + t1 * dk;
+    const float* q2 = qs + t2 * dk;
+    for (int r = 0; r < dk; ++r) {
+      const float4 s4 = *reinterpret_cast<const float4*>(ss + r * dv + c);
+      fma4(o1, q1[r], s4);
+      fma4(o2, q2[r], s4);
+    }
+    float had[4];
+    float* dst = out + (size_t)(t0 + t1) * heads * dv + (size_t)head * dv + c;
+    load4(dst, had);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) had[e] = fmaf(pw[t1 + 1], o1[e], had[e]);
+    store4(dst, had);
+    if (t2 < len) {
+      dst = out + (size_t)(t0 + t2) * heads * dv + (size_t)head * dv + c;
+      load4(dst, had);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) had[e] = fmaf(pw[t2 + 1], o2[e], had[e]);
+      store4(dst, had);
+    }
   }
 }
 
@@ -289,9 +353,10 @@ FE_EXPORT int fe_linear_recurrence_chunked(const void* proj, int dtype, int ld, 
   if (entries <= 0 || n_tokens <= 0) return 0;
   if (dk < 1 || dv < 1 || heads > 65535 || entries > 65535) return FE_ERR_BAD_SHAPE;
   const int chunks = fe_linear_recurrence_chunks(n_tokens, entries);
-  const size_t smem1 = sizeof(float) * ((size_t)2 * LC * (dk + 1) + (size_t)LC * dv + LC * (LC + 1) + LC + 1);
-  const size_t smem3 = sizeof(float) * ((size_t)LC * (dk + 1) + (size_t)dk * dv + LC + 1);
+  const size_t smem1 = sizeof(float) * ((size_t)LC * dk + (size_t)dk * LCP + (size_t)LC * dv + LC * LCP + LC + 4);
+  const size_t smem3 = sizeof(float) * ((size_t)LC * dk + (size_t)dk * dv + LC + 4);
   if (smem1 > 200 * 1024 || smem3 > 200 * 1024) return FE_ERR_TOO_LARGE;
+  if (dv % 4 || (uintptr_t)out % 16 || (uintptr_t)sums % 16) return FE_ERR_BAD_ALIGN;
   int rc = 0;
 #define CHUNKED(TI)                                                                                                   \
   do {                                                                                                                \

@@ -12,7 +12,8 @@
 // act_mul: act(gate) * up for a row [gate | up]; gated_rmsnorm: rms(x) * w * sigmoid(g).
 #include "common.cuh"
 
-#define FE_MAX_STREAMS 8
+#define FE_MAX_STREAMS 16
+#define FE_VEC_STREAMS 8      // the 16-byte form keeps four elements of every stream in registers
 #define FE_NORM_NONE 0
 #define FE_NORM_RMS 1
 #define FE_NORM_LAYER 2
@@ -31,7 +32,7 @@ stream_mix_norm_kernel(float* __restrict__ streams, int S, const TU* __restrict_
   pdl_wait();
   const int r = blockIdx.x;
   const int src = row_map ? row_map[r] : r;
-  if (threadIdx.x < S * S) c_mix[threadIdx.x] = mix ? mix[threadIdx.x] : ((threadIdx.x / S) == (threadIdx.x % S) ? 1.f : 0.f);
+  for (int i = threadIdx.x; i < S * S; i += blockDim.x) c_mix[i] = mix ? mix[i] : ((i / S) == (i % S) ? 1.f : 0.f);
   if (threadIdx.x < S) {
     c_out[threadIdx.x] = (out_coef ? out_coef[threadIdx.x] : 1.f) * update_scale;
     c_in[threadIdx.x] = in_coef ? in_coef[threadIdx.x] : 1.f;
@@ -102,12 +103,12 @@ stream_mix_norm_vec_kernel(float* __restrict__ streams, int S, const TU* __restr
                            int write_streams) {
   extern __shared__ float u_row[];          // [W]
   __shared__ float scratch[33];
-  __shared__ float c_mix[FE_MAX_STREAMS * FE_MAX_STREAMS], c_out[FE_MAX_STREAMS], c_in[FE_MAX_STREAMS];
+  __shared__ float c_mix[FE_VEC_STREAMS * FE_VEC_STREAMS], c_out[FE_VEC_STREAMS], c_in[FE_VEC_STREAMS];
   pdl_trigger();
   pdl_wait();
   const int r = blockIdx.x;
   const int src = row_map ? row_map[r] : r;
-  if (threadIdx.x < S * S) c_mix[threadIdx.x] = mix ? mix[threadIdx.x] : ((threadIdx.x / S) == (threadIdx.x % S) ? 1.f : 0.f);
+  for (int i = threadIdx.x; i < S * S; i += blockDim.x) c_mix[i] = mix ? mix[i] : ((i / S) == (i % S) ? 1.f : 0.f);
   if (threadIdx.x < S) {
     c_out[threadIdx.x] = (out_coef ? out_coef[threadIdx.x] : 1.f) * update_scale;
     c_in[threadIdx.x] = in_coef ? in_coef[threadIdx.x] : 1.f;
@@ -117,20 +118,20 @@ stream_mix_norm_vec_kernel(float* __restrict__ streams, int S, const TU* __restr
   const TU* upd = update ? update + (size_t)src * W : nullptr;
   float total = 0.f;
   for (int i = threadIdx.x * 4; i < W; i += blockDim.x * 4) {
-    float x[FE_MAX_STREAMS][4];
+    float x[FE_VEC_STREAMS][4];
 #pragma unroll
-    for (int s = 0; s < FE_MAX_STREAMS; ++s)
+    for (int s = 0; s < FE_VEC_STREAMS; ++s)
       if (s < S) load4(base + (size_t)s * W + i, x[s]);
     float u[4] = {0.f, 0.f, 0.f, 0.f};
     if (upd) {
       float y[4];
       load4(upd + i, y);
 #pragma unroll
-      for (int t = 0; t < FE_MAX_STREAMS; ++t) {
+      for (int t = 0; t < FE_VEC_STREAMS; ++t) {
         if (t < S) {
           float v[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-          for (int s = 0; s < FE_MAX_STREAMS; ++s)
+          for (int s = 0; s < FE_VEC_STREAMS; ++s)
             if (s < S) {
 #pragma unroll
               for (int e = 0; e < 4; ++e) v[e] = fmaf(c_mix[s * S + t], x[s][e], v[e]);
@@ -145,7 +146,7 @@ stream_mix_norm_vec_kernel(float* __restrict__ streams, int S, const TU* __restr
       }
     } else {
 #pragma unroll
-      for (int t = 0; t < FE_MAX_STREAMS; ++t)
+      for (int t = 0; t < FE_VEC_STREAMS; ++t)
         if (t < S) {
 #pragma unroll
           for (int e = 0; e < 4; ++e) u[e] = fmaf(c_in[t], x[t][e], u[e]);
@@ -197,7 +198,7 @@ FE_EXPORT int fe_stream_mix_norm(float* streams, int n_streams, const void* upda
   int threads = width >= 2048 ? 256 : 128;
   int rc = 0;
   const int update_bytes = update_dtype == FE_DTYPE_F32 ? 16 : 8, out_bytes = out_dtype == FE_DTYPE_F32 ? 16 : 8;
-  const bool vec = (width % 4) == 0 && ((uintptr_t)streams % 16) == 0 && ((uintptr_t)weight % 16) == 0 &&
+  const bool vec = n_streams <= FE_VEC_STREAMS && (width % 4) == 0 && ((uintptr_t)streams % 16) == 0 && ((uintptr_t)weight % 16) == 0 &&
                    ((uintptr_t)update % update_bytes) == 0 && ((uintptr_t)out % out_bytes) == 0;
   if (vec) threads = width >= 1024 ? 256 : width >= 512 ? 128 : 64;
 #define LAUNCH(TU, TO)                                                                                          \

@@ -251,7 +251,7 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, status:
 
 
 NORM_NONE, NORM_RMS, NORM_LAYER = 0, 1, 2
-MAX_STREAMS = 8
+MAX_STREAMS = 16
 
 
 def stream_mix_norm(
@@ -545,8 +545,8 @@ def linear_recurrence(
     assert decay.numel() == heads and out.shape == (proj.shape[0], heads * dv)
     assert slots.dtype == torch.int32 and cu_tokens.dtype == torch.int32
     n = proj.shape[0]
-    fits = 4 * max(2 * 64 * (dk + 1) + 64 * dv + 64 * 65 + 65, 64 * (dk + 1) + dk * dv + 65) <= 200 * 1024
-    if max_new > RECURRENCE_SERIAL_TOKENS and fits:
+    fits = 4 * max(64 * dk + dk * 68 + 64 * dv + 64 * 68 + 68, 64 * dk + dk * dv + 68) <= 200 * 1024
+    if max_new > RECURRENCE_SERIAL_TOKENS and fits and dv % 4 == 0:
         chunks = int(lib().fe_linear_recurrence_chunks(int(n), int(entries)))
         sums = _scratch.get("recurrence chunk states", proj.device, chunks * heads * dk * dv, torch.float32, 1 << 22)
         check(

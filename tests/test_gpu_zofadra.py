@@ -116,6 +116,16 @@ def test_each_mechanism_alone(tmp_path, name, streams, dtype):
     assert_close(got, oracle(cfg, weights, tokens), dtype, name)
 
 
+def test_many_streams(tmp_path):
+    """More copies of the residual stream than the 16-byte form of the kernel keeps in registers."""
+    cfg = pz.config([pz.attention_layer(window=5), pz.lightning_layer()], streams=9)
+    weights = write_model(tmp_path / "m", cfg, 21)
+    tokens = tokens_of(cfg, 21, 5)
+    runner = make_runner(tmp_path / "m", "float32")
+    got = run_schedule(runner, {"a": tokens}, [[("a", 18)], [("a", 3)]])["a"]
+    assert_close(got, oracle(cfg, weights, tokens), "float32", "nine streams")
+
+
 def test_residual_after_every_layer(tmp_path):
     """The residual stream (the sum of its copies) after every layer, in 32-bit."""
     from forge_engine_b200.engine import StepEntry
