@@ -189,7 +189,8 @@ lr_chunk_local_kernel(const TI* __restrict__ proj, int ld, int q_off, int k_off,
   const int t0 = cu_tokens[entry] + local * LC;
   const int len = min(LC, cu_tokens[entry + 1] - t0);
   const float lam = decay[head];
-  for (int i = threadIdx.x; i <= LC; i += blockDim.x) pw[i] = (float)pow((double)lam, (double)i);
+  for (int i = threadIdx.x; i <= LC; i += blockDim.x) pw[i] = powf(lam, (float)i);
+#pragma unroll 8
   for (int i = threadIdx.x; i < LC * dk; i += blockDim.x) {
     const int t = i / dk, d = i - t * dk;
     float q = 0.f, k = 0.f;
@@ -201,6 +202,7 @@ lr_chunk_local_kernel(const TI* __restrict__ proj, int ld, int q_off, int k_off,
     qs[i] = q;
     kt[d * LCP + t] = k;
   }
+#pragma unroll 8
   for (int i = threadIdx.x; i < LC * dv; i += blockDim.x) {
     const int t = i / dv, c = i - t * dv;
     vs[i] = t < len ? lr_act(to_float(proj[(size_t)(t0 + t) * ld + v_off + (size_t)head * dv + c]), act) : 0.f;
@@ -275,15 +277,24 @@ __global__ void lr_chunk_scan_kernel(float* __restrict__ state, const int* __res
   int first = 0;
   for (int e = 0; e < entry; ++e) first += (cu_tokens[e + 1] - cu_tokens[e] + LC - 1) / LC;
   const int chunks = (count + LC - 1) / LC;
-  const double lam = (double)decay[head];
+  // decay^LC for whole chunks, decay^(tokens of the last chunk) for the last: two powers a thread
+  const float whole = powf(decay[head], (float)LC);
+  const float rest = powf(decay[head], (float)(count - (chunks - 1) * LC));
   float* cell = state + ((size_t)slot * heads + head) * dk * dv + i;
   float s = *cell;
-  for (int c = 0; c < chunks; ++c) {
-    float* sum = sums + ((size_t)(first + c) * heads + head) * dk * dv + i;
-    const int len = min(LC, count - c * LC);
-    const float add = *sum;
-    *sum = s;                                            // the state this chunk starts from
-    s = fmaf((float)pow(lam, (double)len), s, add);
+  const size_t stride = (size_t)heads * dk * dv;
+  float* sum = sums + ((size_t)first * heads + head) * dk * dv + i;
+  for (int c0 = 0; c0 < chunks; c0 += 8) {               // eight chunks' sums are fetched before any is replaced
+    float add[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) add[u] = c0 + u < chunks ? sum[(size_t)(c0 + u) * stride] : 0.f;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      if (c0 + u < chunks) {
+        sum[(size_t)(c0 + u) * stride] = s;              // the state this chunk starts from
+        s = fmaf(c0 + u + 1 < chunks ? whole : rest, s, add[u]);
+      }
+    }
   }
   *cell = s;
 }
@@ -305,12 +316,14 @@ lr_chunk_state_kernel(const TI* __restrict__ proj, int ld, int q_off, int act, c
   const int t0 = cu_tokens[entry] + local * LC;
   const int len = min(LC, cu_tokens[entry + 1] - t0);
   const float lam = decay[head];
-  for (int i = threadIdx.x; i <= LC; i += blockDim.x) pw[i] = (float)pow((double)lam, (double)i);
+  for (int i = threadIdx.x; i <= LC; i += blockDim.x) pw[i] = powf(lam, (float)i);
+#pragma unroll 8
   for (int i = threadIdx.x; i < LC * dk; i += blockDim.x) {
     const int t = i / dk, d = i - t * dk;
     qs[i] = t < len ? lr_act(to_float(proj[(size_t)(t0 + t) * ld + q_off + (size_t)head * dk + d]), act) : 0.f;
   }
   const float* src = sums + ((size_t)blockIdx.x * heads + head) * dk * dv;
+#pragma unroll 8
   for (int i = threadIdx.x * 4; i < dk * dv; i += blockDim.x * 4)
     *reinterpret_cast<float4*>(ss + i) = *reinterpret_cast<const float4*>(src + i);
   __syncthreads();
