@@ -528,7 +528,7 @@ DESIGN_SIZES = {
              "latent": {"dim": 64, "rot_dim": 32, "vdim": 64, "q_rank": 768, "kv_rank": 256},
              "recurrence": {"dim": 64, "vdim": 64}},
     "4096": {"width": 4096, "ff": 12288, "heads": 32, "kv_heads": 8, "dim": 128, "window": 1024,
-             "latent": {"dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": 1536, "kv_rank": 256},
+             "latent": {"dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": 1536, "kv_rank": 512},
              "recurrence": {"dim": 128, "vdim": 128}},
 }
 

@@ -3,7 +3,7 @@
 // FE_V_IN_K = 1: the value is the first FE_DV elements of the cached key row (a latent that is
 // key and value at once); then no second tile is loaded.
 //
-// A block of 4 warps owns 64 rows - the (token, query head) pairs of one entry that share one
+// A block of 4 warps (8 for more than 256 value columns) owns 64 rows - the (token, query head) pairs of one entry that share one
 // kv head, token-major - and walks the key tiles its rows can see (causal, optional window),
 // cp.async double-buffered from the cache pages.  S = Q K^T and O += P V run on mma.sync
 // m16n8k16 with 32-bit accumulators; scale, distance bias, mask and the online softmax are
@@ -25,7 +25,12 @@ namespace {
 
 constexpr int DK = FE_DK, DV = FE_DV;
 constexpr bool V_IN_K = FE_V_IN_K != 0;
-constexpr int BM = 64, WARPS = 4;
+constexpr int BM = 64;
+// more than 256 value columns: two groups of four warps share a row tile, each with half the
+// columns (both take the scores; the accumulators of sixteen rows x 512 columns fit no warp)
+constexpr int VSPLIT = DV > 256 ? 2 : 1;
+constexpr int WARPS = 4 * VSPLIT;
+constexpr int DVW = DV / VSPLIT;                // value columns of one warp
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr int BN = DK > 320 ? 32 : 64;
 constexpr int KS = DK + 8;                     // row stride of the Q and K tiles in shared memory
@@ -95,6 +100,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(Params p, 
   const int row0 = tile * BM;
   if (row0 >= rows_total) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int rw = warp & 3, vcol0 = (warp >> 2) * DVW;      // the warp's sixteen rows and first value column
   const int* table = p.table + (size_t)entry * p.max_pages;
 
   // the row tile of Q
@@ -148,19 +154,19 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(Params p, 
   bool row_live[2];
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
-    const int rho = row0 + warp * 16 + quad + 8 * h;
+    const int rho = row0 + rw * 16 + quad + 8 * h;
     row_live[h] = rho < rows_total;
     row_pos[h] = row_live[h] ? start + rho / p.groups : -1;
     row_slope[h] = (row_live[h] && p.slopes) ? p.slopes[kvh * p.groups + rho % p.groups] * LOG2E : 0.f;
   }
   const float scale2 = p.scale * LOG2E;       // scores are kept in units of log 2, so that exp is one exp2
   // rows of this warp, first and last position (all sixteen live), for tiles that need no mask
-  const bool warp_full = row0 + warp * 16 + 15 < rows_total;
-  const int warp_pos_lo = start + (row0 + warp * 16) / p.groups, warp_pos_hi = start + (row0 + warp * 16 + 15) / p.groups;
-  const bool warp_live = row0 + warp * 16 < rows_total;
-  float o[DV / 8][4];
+  const bool warp_full = row0 + rw * 16 + 15 < rows_total;
+  const int warp_pos_lo = start + (row0 + rw * 16) / p.groups, warp_pos_hi = start + (row0 + rw * 16 + 15) / p.groups;
+  const bool warp_live = row0 + rw * 16 < rows_total;
+  float o[DVW / 8][4];
 #pragma unroll
-  for (int n = 0; n < DV / 8; ++n)
+  for (int n = 0; n < DVW / 8; ++n)
 #pragma unroll
     for (int c = 0; c < 4; ++c) o[n][c] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
@@ -195,7 +201,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(Params p, 
 #pragma unroll 2
     for (int kk = 0; kk < DK / 16; ++kk) {
       unsigned a[4];
-      ldsm4(a[0], a[1], a[2], a[3], Qs + (warp * 16 + (lane & 15)) * KS + kk * 16 + (lane >> 4) * 8);
+      ldsm4(a[0], a[1], a[2], a[3], Qs + (rw * 16 + (lane & 15)) * KS + kk * 16 + (lane >> 4) * 8);
 #pragma unroll
       for (int j = 0; j < BN / 8; j += 2) {
         unsigned b0, b1, b2, b3;
@@ -256,7 +262,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(Params p, 
       }
     }
 #pragma unroll
-    for (int n = 0; n < DV / 8; ++n) {
+    for (int n = 0; n < DVW / 8; ++n) {
       o[n][0] *= corr[0]; o[n][1] *= corr[0];
       o[n][2] *= corr[1]; o[n][3] *= corr[1];
     }
@@ -270,9 +276,9 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(Params p, 
       split2(s[2 * ks + 1][0], s[2 * ks + 1][1], hi[2], lo[2]);
       split2(s[2 * ks + 1][2], s[2 * ks + 1][3], hi[3], lo[3]);
 #pragma unroll
-      for (int n = 0; n < DV / 8; n += 2) {
+      for (int n = 0; n < DVW / 8; n += 2) {
         unsigned b0, b1, b2, b3;
-        ldsm4_trans(b0, b1, b2, b3, vd + (ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * vstride + (n + (lane >> 4)) * 8);
+        ldsm4_trans(b0, b1, b2, b3, vd + (ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * vstride + vcol0 + (n + (lane >> 4)) * 8);
         mma16816(o[n], hi, b0, b1);
         mma16816(o[n], lo, b0, b1);
         mma16816(o[n + 1], hi, b2, b3);
@@ -291,13 +297,13 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(Params p, 
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       if (!row_live[h]) continue;
-      const int rho = row0 + warp * 16 + quad + 8 * h;
+      const int rho = row0 + rw * 16 + quad + 8 * h;
       const int token = t_begin + rho / p.groups, head = kvh * p.groups + rho % p.groups;
       bf16* dst = p.out + (size_t)token * p.o_ts + (size_t)head * p.o_hs;
       const float inv = l_run[h] > 0.f ? 1.f / l_run[h] : 0.f;
 #pragma unroll
-      for (int n = 0; n < DV / 8; ++n)
-        *reinterpret_cast<__nv_bfloat162*>(dst + n * 8 + pair * 2) =
+      for (int n = 0; n < DVW / 8; ++n)
+        *reinterpret_cast<__nv_bfloat162*>(dst + vcol0 + n * 8 + pair * 2) =
             __floats2bfloat162_rn(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);
     }
     return;
@@ -306,14 +312,14 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(Params p, 
   float* mine = p.part + ((((size_t)entry * p.tiles + tile) * p.nkv + kvh) * p.splits + split) * (size_t)BM * (DV + 2);
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
-    const int r = warp * 16 + quad + 8 * h;
+    const int r = rw * 16 + quad + 8 * h;
     float* dst = mine + (size_t)r * (DV + 2);
 #pragma unroll
-    for (int n = 0; n < DV / 8; ++n) {
-      dst[n * 8 + pair * 2] = o[n][2 * h];
-      dst[n * 8 + pair * 2 + 1] = o[n][2 * h + 1];
+    for (int n = 0; n < DVW / 8; ++n) {
+      dst[vcol0 + n * 8 + pair * 2] = o[n][2 * h];
+      dst[vcol0 + n * 8 + pair * 2 + 1] = o[n][2 * h + 1];
     }
-    if (pair == 0) {
+    if (pair == 0 && vcol0 == 0) {
       dst[DV] = m_run[h];
       dst[DV + 1] = l_run[h];
     }

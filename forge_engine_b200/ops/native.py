@@ -398,7 +398,7 @@ def qkv_prepare(
 
 
 _general_libs: dict = {}
-GENERAL_MMA_MAX_VALUE = 256     # accumulator registers of a warp's sixteen rows
+GENERAL_MMA_MAX_VALUE = 512     # two warp groups of a block take 256 columns each
 GENERAL_MMA_MAX_KEY = 576
 GENERAL_MMA_ROWS = 64           # (token, head) rows of one block
 
@@ -430,6 +430,7 @@ def general_mma_takes(dtype, key_dim: int, value_dim: int) -> bool:
     """Whether the tensor-core form of the general attention runs for these sizes."""
     return (dtype == torch.bfloat16 and key_dim % 16 == 0 and value_dim % 16 == 0
             and 16 <= key_dim <= GENERAL_MMA_MAX_KEY and 16 <= value_dim <= GENERAL_MMA_MAX_VALUE
+            and (value_dim <= 256 or value_dim % 32 == 0)
             and _os.environ.get("FORGE_ENGINE_GENERAL_MMA", "1") != "0")
 
 

@@ -369,16 +369,19 @@ def test_a_key_far_back_among_hundreds(new_tokens, dtype):
         assert float((got - ref[T - count :]).abs().max()) <= tol, splits
 
 
-def test_tensor_core_attention_with_the_value_inside_the_key():
+@pytest.mark.parametrize("dk, dv", ((48, 32), (320, 288)))
+def test_tensor_core_attention_with_the_value_inside_the_key(dk, dv):
     """One cached vector that is key and value (its first elements), many heads on one kv head,
-    queries and outputs with strides of their own; prompt portion and decoding, with splits."""
+    queries and outputs with strides of their own; prompt portion and decoding, with splits.
+    With more than 256 value columns two warp groups share a tile's columns."""
     from forge_engine_b200.ops import native
 
     gen = torch.Generator().manual_seed(9)
-    T, H, dk, dv, page = 333, 6, 48, 32, 8
+    T, H, page = 333, 6, 8
     q = torch.randn(T, H, dk, generator=gen).to(torch.bfloat16).float()
     kv = torch.randn(T, 1, dk, generator=gen).to(torch.bfloat16).float()
-    ref = plain_attention(q, kv, kv[:, :, :dv], None, None, 0.2)
+    scale = 0.2 * (48 / dk) ** 0.5
+    ref = plain_attention(q, kv, kv[:, :, :dv], None, None, scale)
     device = "cuda"
     pages = -(-T // page)
     order = torch.randperm(pages + 2, generator=gen)[:pages]
@@ -395,7 +398,7 @@ def test_tensor_core_attention_with_the_value_inside_the_key():
         wide[:, :, :dk] = q[first:].to(torch.bfloat16).to(device)
         out = torch.zeros(count, H, dv + 8, dtype=torch.bfloat16, device=device)
         native.attention_general(wide, (H * (dk + 16), dk + 16), cache, dk, cache, dv, out, (H * (dv + 8), dv + 8), table,
-                                 positions, entry, H, None, None, 0.2, status,
+                                 positions, entry, H, None, None, scale, status,
                                  entries=(torch.tensor([0, count], dtype=torch.int32, device=device),
                                           torch.tensor([first], dtype=torch.int32, device=device), 1, count),
                                  splits=splits)
