@@ -71,6 +71,7 @@ struct GemmParams {
   unsigned wait_limit;   // polls a wait may take before the block gives up
   int skip_kblock;       // test fault: the producer leaves out the load of this k-block (-1: none)
   QkvRope rope;          // EPI_QKV_ROPE only
+  int act;               // EPI_SILU_MUL_BF16: 0 SiLU, 1 the tanh form of GELU
 };
 
 template <int BN, int EPI = 0> __host__ __device__ constexpr int stages_for() {
@@ -91,6 +92,12 @@ template <int BN, int EPI = 0> __host__ __device__ constexpr int stages_for() {
   return BN <= 16 ? FE_TC5_STAGES_16 : (BN <= 32 ? 5 : (BN <= 64 ? 4 : (BN == 128 ? 3 : 4)));
 }
 
+// The activation of the gate in the gated epilogue.
+__device__ __forceinline__ float gate_act(float x, int act) {
+  if (act == 0) return silu_f(x);
+  return 0.5f * x * (1.f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+}
+
 // Finished values of one accumulator row (feature) for 16 consecutive tokens.
 template <int EPI>
 __device__ __forceinline__ void store16(const GemmParams& p, float (&v)[16], int feature, int token0, int lane) {
@@ -106,7 +113,7 @@ __device__ __forceinline__ void store16(const GemmParams& p, float (&v)[16], int
       const float send = lane < 16 ? v[j + 1] : v[j];
       const float recv = __shfl_xor_sync(0xffffffffu, send, 16);
       const int token = token0 + j + (lane < 16 ? 0 : 1);
-      const float r = lane < 16 ? silu_f(v[j]) * recv : silu_f(recv) * v[j + 1];
+      const float r = lane < 16 ? gate_act(v[j], p.act) * recv : gate_act(recv, p.act) * v[j + 1];
       if (token < p.n && out_feature < half_o) y[(size_t)token * half_o + out_feature] = __float2bfloat16_rn(r);
     }
     return;
@@ -188,7 +195,7 @@ __device__ __forceinline__ void store_one(const GemmParams& p, float v, int feat
     const int half_o = p.o >> 1;
     const int out_feature = (feature >> 5) * 16 + (lane & 15);
     if (lane < 16 && token < p.n && out_feature < half_o)
-      reinterpret_cast<bf16*>(p.y)[(size_t)token * half_o + out_feature] = __float2bfloat16_rn(silu_f(v) * up);
+      reinterpret_cast<bf16*>(p.y)[(size_t)token * half_o + out_feature] = __float2bfloat16_rn(gate_act(v, p.act) * up);
     return;
   }
   if (feature >= p.o || token >= p.n) return;
@@ -570,7 +577,7 @@ FE_EXPORT void fe_gemm_tc5_set_test_fault(unsigned wait_limit, int skip_kblock) 
 FE_EXPORT int fe_gemm_tc5_tile(int n) { return n <= 16 ? 16 : (n <= 32 ? 32 : (n <= 64 ? 64 : (n <= 128 ? 128 : 256))); }
 
 static int run_gemm(const void* x, const void* w, const float* bias, void* y, int n, int o, int k, int epilogue, int ksplit,
-                    float* ws_part, unsigned* ws_count, int* status, const QkvRope* rope, cudaStream_t stream) {
+                    float* ws_part, unsigned* ws_count, int* status, const QkvRope* rope, cudaStream_t stream, int act = 0) {
   if (n <= 0 || o <= 0) return 0;
   if (k <= 0 || (k % 8) != 0) return FE_ERR_BAD_SHAPE;
   if (epilogue == EPI_SILU_MUL_BF16 && ((o % 32) != 0 || bias != nullptr)) return FE_ERR_BAD_SHAPE;
@@ -599,7 +606,7 @@ static int run_gemm(const void* x, const void* w, const float* bias, void* y, in
     return FE_ERR_BAD_SHAPE;
   const int cluster_reduce = (!atomic_add && ksplit > 1 && ksplit <= 8 && bn <= CLUSTER_REDUCE_TOKENS) ? 1 : 0;
   GemmParams p{y, bias, n, o, k, epilogue, ksplit, cluster_reduce, atomic_add, ws_part, ws_count, status,
-               g_test_wait_limit ? g_test_wait_limit : WAIT_LIMIT, g_test_skip_kblock, rope ? *rope : QkvRope{}};
+               g_test_wait_limit ? g_test_wait_limit : WAIT_LIMIT, g_test_skip_kblock, rope ? *rope : QkvRope{}, act};
   dim3 grid((o + BM - 1) / BM, (n + bn - 1) / bn, ksplit);
   if (grid.y > 65535 || grid.z > 65535) return FE_ERR_TOO_LARGE;
   switch (bn) {
@@ -612,14 +619,20 @@ static int run_gemm(const void* x, const void* w, const float* bias, void* y, in
 }
 
 // epilogue: 0 store bf16 [n, o]; 1 store f32 [n, o]; 2 add into f32 [n, o];
-// 3 y[n, o/2] = silu(gate) * up (bf16) for w whose rows alternate 16 gate, 16 up features.
+// 3 y[n, o/2] = silu(gate) * up (bf16) for w whose rows alternate 16 gate, 16 up features;
+// 5 the same with the tanh form of GELU in place of SiLU.
 // ksplit > 1 needs ws_part (floats: feature tiles * token tiles * ksplit * tile * 128) and
 // ws_count (one zeroed unsigned per output tile; left zeroed).
 FE_EXPORT int fe_gemm_tc5(const void* x, const void* w, const float* bias, void* y, int n, int o, int k,
                           int epilogue, int ksplit, float* ws_part, unsigned* ws_count, int* status,
                           cudaStream_t stream) {
+  int act = 0;
+  if (epilogue == 5) {
+    act = 1;
+    epilogue = EPI_SILU_MUL_BF16;
+  }
   if (epilogue < EPI_STORE_BF16 || epilogue > EPI_SILU_MUL_BF16) return FE_ERR_BAD_DTYPE;
-  return run_gemm(x, w, bias, y, n, o, k, epilogue, ksplit, ws_part, ws_count, status, nullptr, stream);
+  return run_gemm(x, w, bias, y, n, o, k, epilogue, ksplit, ws_part, ws_count, status, nullptr, stream, act);
 }
 
 // The fused q/k/v projection of up to 64 tokens with 128-wide heads: y [n, (nq + 2 nkv) * 128]

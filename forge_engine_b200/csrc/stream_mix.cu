@@ -229,19 +229,29 @@ __device__ __forceinline__ float act_apply(float z, int act) {
   return 0.5f * z * (1.f + tanhf(inner));
 }
 
+// block == 0: a row is [all gate | all up]; block == B > 0: it alternates B gate features, B up
+// features (the layout the fused projection kernels want).
+__device__ __forceinline__ void gate_up_at(int i, int inter, int block, int* gate_at, int* up_at) {
+  if (block == 0) { *gate_at = i; *up_at = inter + i; }
+  else { const int b = i / block; *gate_at = 2 * b * block + (i - b * block); *up_at = *gate_at + block; }
+}
+
 template <typename TI, typename TO>
-__global__ void act_mul_kernel(const TI* __restrict__ gate_up, TO* __restrict__ out, int inter, int act) {
+__global__ void act_mul_kernel(const TI* __restrict__ gate_up, TO* __restrict__ out, int inter, int act, int block) {
   pdl_trigger();
   pdl_wait();
   const int row = blockIdx.x;
   const TI* g = gate_up + (size_t)row * 2 * inter;
   TO* o = out + (size_t)row * inter;
-  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < inter; i += gridDim.y * blockDim.x)
-    o[i] = from_float<TO>(act_apply(to_float(g[i]), act) * to_float(g[inter + i]));
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < inter; i += gridDim.y * blockDim.x) {
+    int ga, ua;
+    gate_up_at(i, inter, block, &ga, &ua);
+    o[i] = from_float<TO>(act_apply(to_float(g[ga]), act) * to_float(g[ua]));
+  }
 }
 
 template <typename TI, typename TO>
-__global__ void act_mul_vec_kernel(const TI* __restrict__ gate_up, TO* __restrict__ out, int inter, int act) {
+__global__ void act_mul_vec_kernel(const TI* __restrict__ gate_up, TO* __restrict__ out, int inter, int act, int block) {
   pdl_trigger();
   pdl_wait();
   const int row = blockIdx.x;
@@ -249,8 +259,10 @@ __global__ void act_mul_vec_kernel(const TI* __restrict__ gate_up, TO* __restric
   TO* o = out + (size_t)row * inter;
   for (int i = (blockIdx.y * blockDim.x + threadIdx.x) * 4; i < inter; i += gridDim.y * blockDim.x * 4) {
     float a[4], b[4];
-    load4(g + i, a);
-    load4(g + inter + i, b);
+    int ga, ua;
+    gate_up_at(i, inter, block, &ga, &ua);      // block is a multiple of 4: four features stay together
+    load4(g + ga, a);
+    load4(g + ua, b);
 #pragma unroll
     for (int e = 0; e < 4; ++e) a[e] = act_apply(a[e], act) * b[e];
     store4(o + i, a);
@@ -258,31 +270,32 @@ __global__ void act_mul_vec_kernel(const TI* __restrict__ gate_up, TO* __restric
 }
 
 FE_EXPORT int fe_act_mul(const void* gate_up, int in_dtype, void* out, int out_dtype, int rows, int inter, int act,
-                         cudaStream_t stream) {
+                         int block, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (act != 0 && act != 1) return FE_ERR_BAD_SHAPE;
+  if (block < 0 || (block > 0 && (inter % block) != 0)) return FE_ERR_BAD_SHAPE;
   const int threads = 256;
-  if ((inter % 4) == 0 && ((uintptr_t)gate_up % 16) == 0 && ((uintptr_t)out % 16) == 0) {
+  if ((inter % 4) == 0 && (block % 4) == 0 && ((uintptr_t)gate_up % 16) == 0 && ((uintptr_t)out % 16) == 0) {
     int pieces = (inter / 4 + threads - 1) / threads;
     if (pieces > 64) pieces = 64;
     dim3 vgrid(rows, pieces);
     if (in_dtype == FE_DTYPE_F32 && out_dtype == FE_DTYPE_F32)
-      return fe_launch_dependent(act_mul_vec_kernel<float, float>, vgrid, dim3(threads), 0, stream, (const float*)gate_up, (float*)out, inter, act);
+      return fe_launch_dependent(act_mul_vec_kernel<float, float>, vgrid, dim3(threads), 0, stream, (const float*)gate_up, (float*)out, inter, act, block);
     if (in_dtype == FE_DTYPE_BF16 && out_dtype == FE_DTYPE_BF16)
-      return fe_launch_dependent(act_mul_vec_kernel<bf16, bf16>, vgrid, dim3(threads), 0, stream, (const bf16*)gate_up, (bf16*)out, inter, act);
+      return fe_launch_dependent(act_mul_vec_kernel<bf16, bf16>, vgrid, dim3(threads), 0, stream, (const bf16*)gate_up, (bf16*)out, inter, act, block);
     if (in_dtype == FE_DTYPE_F32 && out_dtype == FE_DTYPE_BF16)
-      return fe_launch_dependent(act_mul_vec_kernel<float, bf16>, vgrid, dim3(threads), 0, stream, (const float*)gate_up, (bf16*)out, inter, act);
+      return fe_launch_dependent(act_mul_vec_kernel<float, bf16>, vgrid, dim3(threads), 0, stream, (const float*)gate_up, (bf16*)out, inter, act, block);
     return FE_ERR_BAD_DTYPE;
   }
   int chunks = (inter + threads - 1) / threads;
   if (chunks > 64) chunks = 64;
   dim3 grid(rows, chunks);
   if (in_dtype == FE_DTYPE_F32 && out_dtype == FE_DTYPE_F32)
-    return fe_launch_dependent(act_mul_kernel<float, float>, grid, dim3(threads), 0, stream, (const float*)gate_up, (float*)out, inter, act);
+    return fe_launch_dependent(act_mul_kernel<float, float>, grid, dim3(threads), 0, stream, (const float*)gate_up, (float*)out, inter, act, block);
   if (in_dtype == FE_DTYPE_BF16 && out_dtype == FE_DTYPE_BF16)
-    return fe_launch_dependent(act_mul_kernel<bf16, bf16>, grid, dim3(threads), 0, stream, (const bf16*)gate_up, (bf16*)out, inter, act);
+    return fe_launch_dependent(act_mul_kernel<bf16, bf16>, grid, dim3(threads), 0, stream, (const bf16*)gate_up, (bf16*)out, inter, act, block);
   if (in_dtype == FE_DTYPE_F32 && out_dtype == FE_DTYPE_BF16)
-    return fe_launch_dependent(act_mul_kernel<float, bf16>, grid, dim3(threads), 0, stream, (const float*)gate_up, (bf16*)out, inter, act);
+    return fe_launch_dependent(act_mul_kernel<float, bf16>, grid, dim3(threads), 0, stream, (const float*)gate_up, (bf16*)out, inter, act, block);
   return FE_ERR_BAD_DTYPE;
 }
 

@@ -58,7 +58,7 @@ def _declare(handle: ctypes.CDLL) -> None:
     signatures = {
         "fe_embedding": [p, p, i, p, i, i, i, f, i, p, p],
         "fe_stream_mix_norm": [p, i, p, i, f, p, p, p, i, p, f, p, i, p, i, i, i, p],
-        "fe_act_mul": [p, i, p, i, i, i, i, p],
+        "fe_act_mul": [p, i, p, i, i, i, i, i, p],
         "fe_gated_rmsnorm": [p, p, i, i, p, p, i, i, i, f, p],
         "fe_qkv_prepare": [p, i, i, i, i, i, i, p, i, p, i, i, i, i, i, p, i, p, i, i, i, f, p, i, i, p, ll, ll, i,
                            p, p, i, p, i, i, i, p, p, i, p, p],
@@ -303,12 +303,15 @@ def stream_mix_norm(
 ACT_SILU, ACT_GELU_TANH = 0, 1
 
 
-def act_mul(gate_up: torch.Tensor, out: torch.Tensor, act: int) -> None:
-    """out[n, i] = act(gate_up[n, i]) * gate_up[n, inter + i] in 32-bit, rounded on store."""
+def act_mul(gate_up: torch.Tensor, out: torch.Tensor, act: int, block: int = 0) -> None:
+    """out[n, i] = act(gate) * up in 32-bit, rounded on store.  ``block`` 0: a row of
+    ``gate_up`` is all gate features then all up features; ``block`` B: it alternates B gate,
+    B up features."""
     _dense(gate_up, "gate_up"), _dense(out, "out")
     rows, inter = out.shape
     assert gate_up.shape == (rows, 2 * inter)
-    check(lib().fe_act_mul(ptr(gate_up), code(gate_up), ptr(out), code(out), rows, inter, int(act), stream()), "act_mul")
+    check(lib().fe_act_mul(ptr(gate_up), code(gate_up), ptr(out), code(out), rows, inter, int(act), int(block), stream()),
+          "act_mul")
 
 
 def gated_rmsnorm(x: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float) -> None:
@@ -857,6 +860,7 @@ def gemm_simt(
 
 
 TC5_STORE_BF16, TC5_STORE_F32, TC5_ADD_F32, TC5_SILU_MUL = 0, 1, 2, 3
+TC5_GELU_MUL = 5      # the gated epilogue with the tanh form of GELU
 
 
 def tc5_tile(n: int) -> int:
@@ -943,13 +947,14 @@ def gemm_tc5(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int,
     """out = x @ w.T on tcgen05 tensor cores (bfloat16 operands, TMA-fed).
 
     epilogue 0: out bf16 [n, o]; 1: out f32 [n, o]; 2: out f32 [n, o] += product;
-    3: out bf16 [n, o/2] = silu(gate) * up for w whose rows alternate 16 gate, 16 up features.
+    3: out bf16 [n, o/2] = silu(gate) * up for w whose rows alternate 16 gate, 16 up features
+    (5: the same with the tanh form of GELU).
     ``ksplit`` blocks share an output tile (deterministic reduction through a workspace)."""
     _dense(x, "x"), _dense(w, "w"), _dense(out, "out")
     n, k = x.shape
     o = w.shape[0]
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == k
-    if epilogue == TC5_SILU_MUL:
+    if epilogue in (TC5_SILU_MUL, TC5_GELU_MUL):
         assert out.shape == (n, o // 2) and out.dtype == torch.bfloat16
     else:
         assert out.shape == (n, o)

@@ -26,9 +26,8 @@ class GatedMLP(FeedForward):
         self.inter = spec.intermediate_size
         gate, up, down = (local_name(spec, n) for n in ("gate_proj.weight", "up_proj.weight", "down_proj.weight"))
         # Rows of the fused weight alternate 16 gate and 16 up features where the size allows:
-        # the tensor-core kernel then finishes silu(gate) * up in its epilogue.  (Only SiLU
-        # has that epilogue; another activation keeps gate and up rows apart.)
-        self.block = GATE_UP_BLOCK if self.inter % GATE_UP_BLOCK == 0 and self.activation == native.ACT_SILU else 0
+        # the tensor-core kernel then finishes act(gate) * up in its epilogue.
+        self.block = GATE_UP_BLOCK if self.inter % GATE_UP_BLOCK == 0 else 0
         # the sources are looked up one at a time and copied into the fused tensor
         if self.block:
             fused = interleaved_rows(weights, gate, up, self.inter, self.block)
@@ -49,20 +48,20 @@ class GatedMLP(FeedForward):
     def forward_add(self, x, residual) -> bool:
         """``forward`` with the update added into the 32-bit ``residual`` by the down projection
         itself.  False (and nothing done) where that projection cannot."""
-        if not (self.block == 16 and self.down.adds_into(x, residual) and self.gate_up._tc5_ok(x)
+        if not (self.block == 16 and self.activation == native.ACT_SILU and self.down.adds_into(x, residual) and self.gate_up._tc5_ok(x)
                 and self.gate_up.out_features % 32 == 0 and self.gate_up.bias is None):
             return False
         return self.down.add_into(self.gate_up.silu_mul(x, self.block), residual)
 
     def forward(self, x):
-        act = self.gate_up.silu_mul(x, self.block) if self.block else None
+        act = self.gate_up.silu_mul(x, self.block, self.activation) if self.block else None
         if act is None:
             act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
             if self.activation == native.ACT_SILU:
                 native.silu_mul(self.gate_up(x), act, self.block)
             else:
                 # the activation is taken of the 32-bit sums of the projection, not of their rounding
-                native.act_mul(self.gate_up(x, out_dtype=torch.float32), act, self.activation)
+                native.act_mul(self.gate_up(x, out_dtype=torch.float32), act, self.activation, self.block)
         return self.down(act)
 
 
