@@ -3,7 +3,7 @@
 // a bias on the distance between query and key, queries and outputs laid out with any
 // strides.  Two kernels:
 //
-// qkv_prepare - one block per token: reads the token's projected q, k (and v), normalises
+// qkv_prepare - one block per token and side (queries; keys and values): reads the token's projected q, k (and v), normalises
 //   (per head over the head's leading elements, or over the whole projection at once, or not
 //   at all), rotates a stretch of every head by the step's cosine/sine table, stores the
 //   queries where the attention kernel wants them and k, v into their cache pages.
@@ -86,18 +86,21 @@ qkv_prepare_kernel(PrepSide q, PrepSide k, const TI* __restrict__ v_in, int v_in
   pdl_trigger();
   pdl_wait();
   const int token = blockIdx.x;
+  // with both sides present a token has two blocks: one for the queries, one for keys and values
+  const bool do_q = q.in != nullptr && (gridDim.y == 1 ? true : blockIdx.y == 0);
+  const bool do_k = k.in != nullptr && (gridDim.y == 1 ? true : blockIdx.y == 1);
   const int q_total = q.in ? q.heads * q.dim : 0, k_total = k.in ? k.heads * k.dim : 0;
   float* q_row = rows;
-  float* k_row = rows + q_total;
+  float* k_row = rows + (gridDim.y == 1 ? q_total : 0);
   const float2* angles = table ? table + (size_t)token * (rot_dims >> 1) : nullptr;
-  if (q.in) {
+  if (do_q) {
     const TI* src = (const TI*)q.in + (size_t)token * q.in_stride;
     for (int i = threadIdx.x; i < q_total; i += blockDim.x) {
       const int h = i / q.dim;
       q_row[i] = to_float(src[(size_t)h * q.head_stride + (i - h * q.dim)]);
     }
   }
-  if (k.in) {
+  if (do_k) {
     const TI* src = (const TI*)k.in + (size_t)token * k.in_stride;
     for (int i = threadIdx.x; i < k_total; i += blockDim.x) {
       const int h = i / k.dim;
@@ -105,7 +108,7 @@ qkv_prepare_kernel(PrepSide q, PrepSide k, const TI* __restrict__ v_in, int v_in
     }
   }
   __syncthreads();
-  if (q.in) {
+  if (do_q) {
     prep_norm_rotate(q_row, q, eps, angles, rot_dims, interleaved, scratch);
     TC* dst = q_out + (size_t)token * q_out_token_stride + q_out_dim_offset;
     for (int i = threadIdx.x; i < q_total; i += blockDim.x) {
@@ -113,7 +116,7 @@ qkv_prepare_kernel(PrepSide q, PrepSide k, const TI* __restrict__ v_in, int v_in
       dst[(size_t)h * q_out_head_stride + d] = from_float<TC>(q_row[i]);
     }
   }
-  if (!k.in) return;
+  if (!do_k) return;
   prep_norm_rotate(k_row, k, eps, angles, rot_dims, interleaved, scratch);
   const int pos = positions[token], entry = token_entry[token];
   const int logical = pos / page_size;
@@ -153,14 +156,16 @@ FE_EXPORT int fe_qkv_prepare(const void* q_in, int q_in_stride, int q_head_strid
   if (rot_dims % 2 || (q_in && q_rot_off >= 0 && q_rot_off + rot_dims > q_dim) || (k_in && k_rot_off >= 0 && k_rot_off + rot_dims > k_dim)) return FE_ERR_BAD_SHAPE;
   PrepSide q{q_in, q_in_stride, q_head_stride > 0 ? q_head_stride : q_dim, q_heads, q_dim, q_norm_mode, q_norm_dims, q_norm_w, q_rot_off};
   PrepSide k{k_in, k_in_stride, k_dim, k_heads, k_dim, k_norm_mode, k_norm_dims, k_norm_w, k_rot_off};
-  const size_t smem = sizeof(float) * ((q_in ? (size_t)q_heads * q_dim : 0) + (k_in ? (size_t)k_heads * k_dim : 0));
+  const size_t q_floats = q_in ? (size_t)q_heads * q_dim : 0, k_floats = k_in ? (size_t)k_heads * k_dim : 0;
+  const int sides = (q_in && k_in) ? 2 : 1;
+  const size_t smem = sizeof(float) * (q_floats > k_floats ? q_floats : k_floats);
   if (smem > 200 * 1024) return FE_ERR_TOO_LARGE;
   int rc = 0;
 #define LAUNCH(TI, TC)                                                                                              \
   do {                                                                                                              \
     if (smem > 48 * 1024)                                                                                           \
       cudaFuncSetAttribute(qkv_prepare_kernel<TI, TC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
-    rc = fe_launch_dependent(qkv_prepare_kernel<TI, TC>, dim3(n_tokens), dim3(256), smem, stream, q, k,             \
+    rc = fe_launch_dependent(qkv_prepare_kernel<TI, TC>, dim3(n_tokens, sides), dim3(256), smem, stream, q, k,             \
                              (const TI*)v_in, v_in_stride, v_dim, eps, (const float2*)table, rot_dims, interleaved, \
                              (TC*)q_out, q_out_token_stride, q_out_head_stride, q_out_dim_offset, (TC*)k_cache,     \
                              (TC*)v_cache, block_table, max_pages, page_size, num_pages, positions, token_entry,    \

@@ -326,7 +326,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(Params p, 
   }
 }
 
-constexpr int MERGE_ROWS = 4, MAX_SPLITS = 32;
+constexpr int MERGE_ROWS = 4, MAX_SPLITS = 32;      // a merge block has four warps, a warp has 32 lanes
 
 // A block combines MERGE_ROWS rows of one row tile: the splits' weights once per row (in a
 // fixed order), then every value column.
@@ -343,18 +343,20 @@ __global__ void __launch_bounds__(128) attention_mma_merge_kernel(Params p) {
   if (first >= rows_total) return;
   const float* base = p.part + (((size_t)entry * p.tiles + tile) * p.nkv + kvh) * p.splits * (size_t)BM * (DV + 2);
   const int rows = min(MERGE_ROWS, rows_total - first);
-  if (threadIdx.x < rows) {
-    const int r = piece * MERGE_ROWS + threadIdx.x;
-    float big = -INFINITY;
-    for (int s = 0; s < p.splits; ++s) big = fmaxf(big, base[((size_t)s * BM + r) * (DV + 2) + DV]);
-    float den = 0.f;
-    for (int s = 0; s < p.splits; ++s) {
-      const float* row = base + ((size_t)s * BM + r) * (DV + 2);
-      const float f = row[DV] == -INFINITY ? 0.f : exp2f(row[DV] - big);      // maxima are in units of log 2
-      weight[threadIdx.x][s] = f;
-      den = fmaf(row[DV + 1], f, den);
+  {
+    // a warp per row, a lane per split: maxima and normalisers are fetched side by side
+    const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (w < rows) {
+      const int r = piece * MERGE_ROWS + w;
+      const float* row = base + ((size_t)lane * BM + r) * (DV + 2);
+      const float m = lane < p.splits ? row[DV] : -INFINITY;
+      const float l = lane < p.splits ? row[DV + 1] : 0.f;
+      const float big = warp_max(m);
+      const float f = m == -INFINITY ? 0.f : exp2f(m - big);      // maxima are in units of log 2
+      const float den = warp_sum(l * f);
+      if (lane < p.splits) weight[w][lane] = f;
+      if (lane == 0) inverse[w] = den > 0.f ? 1.f / den : 0.f;
     }
-    inverse[threadIdx.x] = den > 0.f ? 1.f / den : 0.f;
   }
   __syncthreads();
   for (int idx = threadIdx.x; idx < rows * DV; idx += blockDim.x) {
