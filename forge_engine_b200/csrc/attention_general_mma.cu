@@ -279,9 +279,9 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(Params p, 
       for (int n = 0; n < DVW / 8; n += 2) {
         unsigned b0, b1, b2, b3;
         ldsm4_trans(b0, b1, b2, b3, vd + (ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * vstride + vcol0 + (n + (lane >> 4)) * 8);
-        mma16816(o[n], hi, b0, b1);
+        mma16816(o[n], hi, b0, b1);             // neighbours alternate, so that no product waits
+        mma16816(o[n + 1], hi, b2, b3);         // for the one just issued into its accumulator
         mma16816(o[n], lo, b0, b1);
-        mma16816(o[n + 1], hi, b2, b3);
         mma16816(o[n + 1], lo, b2, b3);
       }
     }
