@@ -37,7 +37,7 @@ constexpr int THREADS = 192;
 // block (tokens x 128 features) must fit in its ring of stages (128 tokens: 64 of 96 KB).
 constexpr int CLUSTER_REDUCE_TOKENS = 128;
 
-enum Epilogue { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_ADD_F32 = 2, EPI_SILU_MUL_BF16 = 3, EPI_QKV_ROPE = 4 };
+enum Epilogue { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_ADD_F32 = 2, EPI_SILU_MUL_BF16 = 3, EPI_QKV_ROPE = 4, EPI_GELU_MUL_BF16 = 5 };
 
 // What the fused q/k/v projection needs beyond the product (EPI_QKV_ROPE; head size 128, so
 // that a 128-feature tile is one head): per-head RMS norm of q and k with one [128] weight
@@ -71,7 +71,6 @@ struct GemmParams {
   unsigned wait_limit;   // polls a wait may take before the block gives up
   int skip_kblock;       // test fault: the producer leaves out the load of this k-block (-1: none)
   QkvRope rope;          // EPI_QKV_ROPE only
-  int act;               // EPI_SILU_MUL_BF16: 0 SiLU, 1 the tanh form of GELU
 };
 
 template <int BN, int EPI = 0> __host__ __device__ constexpr int stages_for() {
@@ -92,16 +91,17 @@ template <int BN, int EPI = 0> __host__ __device__ constexpr int stages_for() {
   return BN <= 16 ? FE_TC5_STAGES_16 : (BN <= 32 ? 5 : (BN <= 64 ? 4 : (BN == 128 ? 3 : 4)));
 }
 
-// The activation of the gate in the gated epilogue.
-__device__ __forceinline__ float gate_act(float x, int act) {
-  if (act == 0) return silu_f(x);
-  return 0.5f * x * (1.f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+// The gate's activation of the gated epilogues: SiLU, or the tanh form of GELU.  Chosen at
+// compile time, so that each instantiation holds the code of one.
+template <int EPI> __device__ __forceinline__ float gate_act(float x) {
+  if (EPI == EPI_GELU_MUL_BF16) return 0.5f * x * (1.f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+  return silu_f(x);
 }
 
 // Finished values of one accumulator row (feature) for 16 consecutive tokens.
 template <int EPI>
 __device__ __forceinline__ void store16(const GemmParams& p, float (&v)[16], int feature, int token0, int lane) {
-  if (EPI == EPI_SILU_MUL_BF16) {
+  if (EPI == EPI_SILU_MUL_BF16 || EPI == EPI_GELU_MUL_BF16) {
     // weight rows alternate 16 gate features, 16 up features: lanes 0-15 hold gate,
     // lanes 16-31 the matching up.  The lower half-warp finishes even tokens, the upper
     // half odd ones, so both halves store.
@@ -113,7 +113,7 @@ __device__ __forceinline__ void store16(const GemmParams& p, float (&v)[16], int
       const float send = lane < 16 ? v[j + 1] : v[j];
       const float recv = __shfl_xor_sync(0xffffffffu, send, 16);
       const int token = token0 + j + (lane < 16 ? 0 : 1);
-      const float r = lane < 16 ? gate_act(v[j], p.act) * recv : gate_act(recv, p.act) * v[j + 1];
+      const float r = lane < 16 ? gate_act<EPI>(v[j]) * recv : gate_act<EPI>(recv) * v[j + 1];
       if (token < p.n && out_feature < half_o) y[(size_t)token * half_o + out_feature] = __float2bfloat16_rn(r);
     }
     return;
@@ -189,13 +189,13 @@ __device__ __forceinline__ void rope_token(const GemmParams& p, float v, int hea
 // lanes of the warp call it for the same token.
 template <int EPI>
 __device__ __forceinline__ void store_one(const GemmParams& p, float v, int feature, int token, int lane) {
-  if (EPI == EPI_SILU_MUL_BF16) {
+  if (EPI == EPI_SILU_MUL_BF16 || EPI == EPI_GELU_MUL_BF16) {
     // lanes 0-15 hold 16 gate features, lanes 16-31 the matching up features
     const float up = __shfl_xor_sync(0xffffffffu, v, 16);
     const int half_o = p.o >> 1;
     const int out_feature = (feature >> 5) * 16 + (lane & 15);
     if (lane < 16 && token < p.n && out_feature < half_o)
-      reinterpret_cast<bf16*>(p.y)[(size_t)token * half_o + out_feature] = __float2bfloat16_rn(gate_act(v, p.act) * up);
+      reinterpret_cast<bf16*>(p.y)[(size_t)token * half_o + out_feature] = __float2bfloat16_rn(gate_act<EPI>(v) * up);
     return;
   }
   if (feature >= p.o || token >= p.n) return;
@@ -551,6 +551,7 @@ int launch_bn(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p,
     case EPI_STORE_F32: return launch_one<BN, EPI_STORE_F32>(mw, mx, p, grid, stream);
     case EPI_ADD_F32: return launch_one<BN, EPI_ADD_F32>(mw, mx, p, grid, stream);
     case EPI_SILU_MUL_BF16: return launch_one<BN, EPI_SILU_MUL_BF16>(mw, mx, p, grid, stream);
+    case EPI_GELU_MUL_BF16: return launch_one<BN, EPI_GELU_MUL_BF16>(mw, mx, p, grid, stream);
     case EPI_QKV_ROPE:
       if (BN <= 64) return launch_one<(BN <= 64 ? BN : 16), EPI_QKV_ROPE>(mw, mx, p, grid, stream);
       return FE_ERR_BAD_SHAPE;
@@ -577,10 +578,10 @@ FE_EXPORT void fe_gemm_tc5_set_test_fault(unsigned wait_limit, int skip_kblock) 
 FE_EXPORT int fe_gemm_tc5_tile(int n) { return n <= 16 ? 16 : (n <= 32 ? 32 : (n <= 64 ? 64 : (n <= 128 ? 128 : 256))); }
 
 static int run_gemm(const void* x, const void* w, const float* bias, void* y, int n, int o, int k, int epilogue, int ksplit,
-                    float* ws_part, unsigned* ws_count, int* status, const QkvRope* rope, cudaStream_t stream, int act = 0) {
+                    float* ws_part, unsigned* ws_count, int* status, const QkvRope* rope, cudaStream_t stream) {
   if (n <= 0 || o <= 0) return 0;
   if (k <= 0 || (k % 8) != 0) return FE_ERR_BAD_SHAPE;
-  if (epilogue == EPI_SILU_MUL_BF16 && ((o % 32) != 0 || bias != nullptr)) return FE_ERR_BAD_SHAPE;
+  if ((epilogue == EPI_SILU_MUL_BF16 || epilogue == EPI_GELU_MUL_BF16) && ((o % 32) != 0 || bias != nullptr)) return FE_ERR_BAD_SHAPE;
   if ((((uintptr_t)x) | ((uintptr_t)w)) & 15) return FE_ERR_BAD_ALIGN;
   if (ksplit < 1) ksplit = 1;
   const int kblocks = (k + BK - 1) / BK;
@@ -606,7 +607,7 @@ static int run_gemm(const void* x, const void* w, const float* bias, void* y, in
     return FE_ERR_BAD_SHAPE;
   const int cluster_reduce = (!atomic_add && ksplit > 1 && ksplit <= 8 && bn <= CLUSTER_REDUCE_TOKENS) ? 1 : 0;
   GemmParams p{y, bias, n, o, k, epilogue, ksplit, cluster_reduce, atomic_add, ws_part, ws_count, status,
-               g_test_wait_limit ? g_test_wait_limit : WAIT_LIMIT, g_test_skip_kblock, rope ? *rope : QkvRope{}, act};
+               g_test_wait_limit ? g_test_wait_limit : WAIT_LIMIT, g_test_skip_kblock, rope ? *rope : QkvRope{}};
   dim3 grid((o + BM - 1) / BM, (n + bn - 1) / bn, ksplit);
   if (grid.y > 65535 || grid.z > 65535) return FE_ERR_TOO_LARGE;
   switch (bn) {
@@ -626,13 +627,8 @@ static int run_gemm(const void* x, const void* w, const float* bias, void* y, in
 FE_EXPORT int fe_gemm_tc5(const void* x, const void* w, const float* bias, void* y, int n, int o, int k,
                           int epilogue, int ksplit, float* ws_part, unsigned* ws_count, int* status,
                           cudaStream_t stream) {
-  int act = 0;
-  if (epilogue == 5) {
-    act = 1;
-    epilogue = EPI_SILU_MUL_BF16;
-  }
-  if (epilogue < EPI_STORE_BF16 || epilogue > EPI_SILU_MUL_BF16) return FE_ERR_BAD_DTYPE;
-  return run_gemm(x, w, bias, y, n, o, k, epilogue, ksplit, ws_part, ws_count, status, nullptr, stream, act);
+  if ((epilogue < EPI_STORE_BF16 || epilogue > EPI_SILU_MUL_BF16) && epilogue != EPI_GELU_MUL_BF16) return FE_ERR_BAD_DTYPE;
+  return run_gemm(x, w, bias, y, n, o, k, epilogue, ksplit, ws_part, ws_count, status, nullptr, stream);
 }
 
 // The fused q/k/v projection of up to 64 tokens with 128-wide heads: y [n, (nq + 2 nkv) * 128]
