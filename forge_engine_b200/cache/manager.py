@@ -25,12 +25,19 @@ from .pages import BlockTable, PagePool, StateSlots
 class PagedKVSpec:
     """Keys and values of ``num_kv_heads`` heads of ``head_dim``; ``window`` None keeps all.
     ``v_head_dim``: size of a value head where it differs (None: ``head_dim``; 0: the run
-    keeps one vector per token and head, no second one - a latent that is key and value)."""
+    keeps one vector per token and head, no second one - a latent that is key and value).
+    ``keep_first``: with a window, positions below it stay visible for ever, so the pages
+    that hold them are never given back."""
 
     num_kv_heads: int
     head_dim: int
     window: int | None = None
     v_head_dim: int | None = None
+    keep_first: int = 0
+
+    def kept_pages(self, page_size: int) -> int:
+        """Leading pages a window never releases."""
+        return 0 if self.window is None or self.keep_first <= 0 else _ceil_div(self.keep_first, page_size)
 
     @property
     def value_dim(self) -> int:
@@ -290,7 +297,8 @@ class CacheManager:
             dead_pages = max(0, first_needed) // self.page_size
             dead_pages = min(dead_pages, len(table.pages))
             released = []
-            for index in range(table.first_live, dead_pages):
+            # pages that hold kept first tokens stay; ``first_live`` counts from behind them
+            for index in range(max(table.first_live, group.spec.kept_pages(self.page_size)), dead_pages):
                 if table.pages[index] >= 0:
                     released.append(table.pages[index])
                     table.pages[index] = -1
@@ -322,7 +330,7 @@ class CacheManager:
                 out.append(full)
             else:
                 span = window - 1 + max_portion  # live keys just before a step's release
-                out.append(min(full, _ceil_div(span, self.page_size) + 1))
+                out.append(min(full, _ceil_div(span, self.page_size) + 1 + group.spec.kept_pages(self.page_size)))
         return out
 
     def free_pages(self) -> list:

@@ -78,7 +78,7 @@ class BlockTable:
         self.first_live = 0
 
     def live_pages(self) -> list[int]:
-        return [p for p in self.pages[self.first_live:] if p >= 0]
+        return [p for p in self.pages if p >= 0]
 
     def __len__(self) -> int:
         return len(self.pages)

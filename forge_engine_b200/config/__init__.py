@@ -11,6 +11,7 @@ from .registry import (
 )
 from .specs import (
     AttentionSpec,
+    DifferentialSpec,
     GatedMLPSpec,
     LatentAttentionSpec,
     LayerNormSpec,
@@ -20,9 +21,11 @@ from .specs import (
     NoPositionSpec,
     NormSpec,
     RotarySpec,
+    RoutedMLPSpec,
     RunSpec,
     StreamMixSpec,
 )
+from .tekilorn import TekilornConfig
 from .zofadra import ZofadraConfig
 
 register_architecture(
@@ -33,10 +36,15 @@ register_architecture(
     Architecture("Zofadra", ZofadraConfig.from_dict, ZofadraConfig.to_model_spec),
     replace=True,
 )
+register_architecture(
+    Architecture("Tekilorn", TekilornConfig.from_dict, TekilornConfig.to_model_spec),
+    replace=True,
+)
 
 __all__ = [
     "Architecture",
     "AttentionSpec",
+    "DifferentialSpec",
     "EngineConfig",
     "GatedMLPSpec",
     "LatentAttentionSpec",
@@ -48,9 +56,11 @@ __all__ = [
     "NormSpec",
     "Qwen3Config",
     "RotarySpec",
+    "RoutedMLPSpec",
     "RunSpec",
     "SchedulerConfig",
     "StreamMixSpec",
+    "TekilornConfig",
     "ZofadraConfig",
     "architecture_of",
     "known_architectures",

@@ -98,6 +98,31 @@ class AttentionSpec:
     # slopes 2^(-8 (h + 1) / H)).
     distance_bias_base: float | None = None
     rename: tuple = ()
+    # With a window: keys at positions below ``keep_first`` stay visible to every later query
+    # (at their true positions), and their cache pages are never given back.
+    keep_first: int = 0
+    # None, or c: scores become c * tanh(score / c) before the softmax.
+    softcap: float | None = None
+    # None, or (coef, every): the scores of a query at position p are multiplied by
+    # 1 + coef * ln(floor((p + 1) / every) + 1).
+    query_temperature: tuple | None = None
+    # True: head h's output is multiplied by sigmoid(w_h . x), x the mixer's input; the
+    # checkpoint holds ``gate_proj.weight`` [heads, hidden].
+    head_gate: bool = False
+    # None, or a DifferentialSpec: every head has two score maps over the same values.
+    differential: object = None
+
+
+@dataclass(frozen=True)
+class DifferentialSpec:
+    """Two softmax maps per head, from two queries and two keys of ``head_dim`` each (a head's
+    projection rows are [map 1, map 2]), over the same values: o = a1 - lambda a2 with
+    lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + offset, one number for the layer from four
+    vectors of ``head_dim`` in the checkpoint; then o / sqrt(mean(o^2) + eps) over the head's
+    values, times (1 - offset)."""
+
+    offset: float
+    eps: float
 
 
 @dataclass(frozen=True)
@@ -148,8 +173,35 @@ class GatedMLPSpec:
 
     hidden_size: int
     intermediate_size: int
-    activation: str = "silu"      # "silu" or "gelu_tanh"
+    # "silu", "gelu_tanh", or "clamped_swish": g' sigmoid(slope g') (u' + 1) in place of
+    # act(g) u, with g' = min(g, limit) and u' = clamp(u, -limit, limit)
+    activation: str = "silu"
     kind: str = "gated_mlp"
+    rename: tuple = ()
+    limit: float | None = None
+    slope: float = 1.0
+
+
+@dataclass(frozen=True)
+class RoutedMLPSpec:
+    """A routed feed-forward: ``experts`` gated units (``expert``: a GatedMLPSpec; tensors
+    ``e<i>.<name>``) of which every token uses the ``top`` with the largest router scores.
+    ``score``: "sigmoid" or "softmax" of the router's 32-bit logits; ``renormalise``: the
+    chosen scores are divided by their sum; ``weight_on`` "input": the unit runs on
+    weight * x, "output": its result is multiplied.  ``shared`` (a GatedMLPSpec or None;
+    tensors ``shared.<name>``) runs for every token and is added, times
+    sigmoid(``shared.sg`` . x) when ``shared_gate``."""
+
+    hidden_size: int
+    experts: int
+    top: int
+    expert: object
+    shared: object = None
+    score: str = "sigmoid"
+    renormalise: bool = False
+    weight_on: str = "input"
+    shared_gate: bool = False
+    kind: str = "routed_mlp"
     rename: tuple = ()
 
 
@@ -196,6 +248,9 @@ class RunSpec:
 
     layer: int
     cache_of: int | None = None
+    # None, or (tensor name, row): that row of a [rows, hidden] tensor of the checkpoint is
+    # added to the residual stream right before this run.
+    shift: tuple | None = None
 
 
 @dataclass(frozen=True)
@@ -215,3 +270,5 @@ class ModelSpec:
     head_name: str = "lm_head.weight"
     embedding_scale: float = 1.0     # the embedding rows are multiplied by this
     residual_streams: int = 1        # copies of the residual stream (see StreamMixSpec)
+    # tensors of the checkpoint that belong to no layer: (name, shape, role) each
+    extra_tensors: tuple = ()

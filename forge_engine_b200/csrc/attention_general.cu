@@ -198,7 +198,24 @@ struct GeneralAttn {
   const float* slopes;      // per query head, or null: s -= slope * (pos - key)
   int window;
   float scale;
+  // What the plain layer does not have (all off when zero / null):
+  int keep_first;           // with a window: keys below this position stay visible to every query
+  float softcap;            // s <- softcap * tanh(s / softcap), before the bias
+  float temp_coef;          // scores of a query at position p are multiplied by
+  int temp_every;           //   1 + temp_coef * ln(floor((p + 1) / temp_every) + 1)
+  int parts;                // score maps per head over shared values (1: the plain layer): part m of
+  long long q_part_stride;  //   a head reads its query q_part_stride * m elements further on, its key
+  int k_part_stride;        //   k_part_stride * m elements into the cached row, and writes
+  long long o_part_stride;  //   o_part_stride * m elements further on
+  const float* gate;        // or null: the row (token, head) is multiplied by sigmoid(gate[token * gate_stride + head])
+  long long gate_stride;
+  int out_f32;              // the output is 32-bit whatever the cache holds
 };
+
+// 1 + coef * ln(floor((p + 1) / every) + 1): what a query's scores are multiplied by
+__device__ __forceinline__ float query_temperature(int pos, float coef, int every) {
+  return every > 0 ? 1.f + coef * logf((float)((pos + 1) / every + 1)) : 1.f;
+}
 
 template <typename T, int RMAX, int NV>
 __global__ void __launch_bounds__(GA_WARPS * 32)
@@ -207,7 +224,7 @@ attention_general_kernel(GeneralAttn a, int* status) {
   pdl_trigger();
   pdl_wait();
   const int groups = a.num_q_heads / a.num_kv_heads;
-  const int token = blockIdx.x, kvh = blockIdx.y;
+  const int token = blockIdx.x, kvh = blockIdx.y / a.parts, part = blockIdx.y - kvh * a.parts;
   const int first = blockIdx.z * RMAX;                  // first of this block's heads inside the kv head's group
   const int R = min(RMAX, groups - first);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -222,7 +239,8 @@ attention_general_kernel(GeneralAttn a, int* status) {
 
   for (int i = threadIdx.x; i < R * a.k_dim; i += blockDim.x) {
     const int r = i / a.k_dim, d = i - r * a.k_dim;
-    qs[i] = to_float(((const T*)a.q)[(size_t)token * a.q_token_stride + (size_t)(head0 + r) * a.q_head_stride + d]);
+    qs[i] = to_float(((const T*)a.q)[(size_t)token * a.q_token_stride + (size_t)(head0 + r) * a.q_head_stride
+                                     + (size_t)part * a.q_part_stride + d]);
   }
   __syncthreads();
 
@@ -240,11 +258,17 @@ attention_general_kernel(GeneralAttn a, int* status) {
   }
 
   const int n_keys = pos - lo + 1;
-  const int n_chunks = (n_keys + 31) >> 5;
-  const bool vec = (a.k_row % 8) == 0 && (a.k_dim % 8) == 0 && ((uintptr_t)a.k % 32) == 0;
+  // keys the window has passed but that stay visible: [0, n_sink), in chunks of their own ahead of the rest
+  const int n_sink = a.window > 0 ? min(a.keep_first, lo) : 0;
+  const int sink_chunks = (n_sink + 31) >> 5;
+  const int n_chunks = sink_chunks + ((n_keys + 31) >> 5);
+  const float row_scale = a.scale * query_temperature(pos, a.temp_coef, a.temp_every);
+  const float inv_cap = a.softcap > 0.f ? 1.f / a.softcap : 0.f;
+  const bool vec = (a.k_row % 8) == 0 && (a.k_dim % 8) == 0 && (a.k_part_stride % 8) == 0 && ((uintptr_t)a.k % 32) == 0;
   for (int c = warp; c < n_chunks; c += GA_WARPS) {
-    const int key = lo + (c << 5) + lane;
-    bool valid = key <= pos;
+    const bool sink = c < sink_chunks;
+    const int key = sink ? (c << 5) + lane : lo + ((c - sink_chunks) << 5) + lane;
+    bool valid = sink ? key < n_sink : key <= pos;
     long long row = -1;                                   // (page, head, slot) as a row index
     if (valid) {
       const int logical = key / a.page_size;
@@ -261,7 +285,7 @@ attention_general_kernel(GeneralAttn a, int* status) {
 #pragma unroll
     for (int r = 0; r < RMAX; ++r) s[r] = 0.f;
     if (valid) {
-      const T* kp = (const T*)a.k + row * a.k_row;
+      const T* kp = (const T*)a.k + row * a.k_row + part * a.k_part_stride;
       if (vec) {
         for (int d = 0; d < a.k_dim; d += 8) {
           float kk[8];
@@ -288,7 +312,9 @@ attention_general_kernel(GeneralAttn a, int* status) {
     const float dist = (float)(pos - key);
 #pragma unroll
     for (int r = 0; r < RMAX; ++r) {
-      const float sc = valid ? s[r] * a.scale - slope[r] * dist : -INFINITY;
+      float sc = s[r] * row_scale;
+      if (a.softcap > 0.f) sc = a.softcap * tanhf(sc * inv_cap);
+      sc = valid ? sc - slope[r] * dist : -INFINITY;
       const float m_new = fmaxf(m[r], warp_max(sc));
       p[r] = valid ? expf(sc - m_new) : 0.f;
       const float corr = (m[r] == -INFINITY) ? 0.f : expf(m[r] - m_new);
@@ -297,7 +323,7 @@ attention_general_kernel(GeneralAttn a, int* status) {
 #pragma unroll
       for (int i = 0; i < NV; ++i) acc[r][i] *= corr;
     }
-    const int in_chunk = min(32, n_keys - (c << 5));
+    const int in_chunk = sink ? min(32, n_sink - (c << 5)) : min(32, n_keys - ((c - sink_chunks) << 5));
     for (int j = 0; j < in_chunk; ++j) {
       const long long rj = __shfl_sync(0xffffffffu, row, j);
       float pj[RMAX];
@@ -340,15 +366,18 @@ attention_general_kernel(GeneralAttn a, int* status) {
       num = fmaf(part_acc[((size_t)w * RMAX + r) * a.v_dim + d], f, num);
       den = fmaf(part_l[w * RMAX + r], f, den);
     }
-    ((T*)a.out)[(size_t)token * a.o_token_stride + (size_t)(head0 + r) * a.o_head_stride + d] =
-        from_float<T>(den > 0.f ? num / den : 0.f);
+    float value = den > 0.f ? num / den : 0.f;
+    if (a.gate) value *= 1.f / (1.f + expf(-a.gate[(size_t)token * a.gate_stride + head0 + r]));
+    const size_t at = (size_t)token * a.o_token_stride + (size_t)(head0 + r) * a.o_head_stride + (size_t)part * a.o_part_stride + d;
+    if (a.out_f32) ((float*)a.out)[at] = value;
+    else ((T*)a.out)[at] = from_float<T>(value);
   }
 }
 
 template <typename T, int RMAX, int NV>
 static int launch_general(const GeneralAttn& a, int n_tokens, int* status, cudaStream_t stream) {
   const int groups = a.num_q_heads / a.num_kv_heads;
-  dim3 grid(n_tokens, a.num_kv_heads, (groups + RMAX - 1) / RMAX);
+  dim3 grid(n_tokens, a.num_kv_heads * a.parts, (groups + RMAX - 1) / RMAX);
   const size_t smem = sizeof(float) * ((size_t)RMAX * a.k_dim + (size_t)GA_WARPS * RMAX * a.v_dim + 2 * GA_WARPS * RMAX);
   if (smem > 200 * 1024) return FE_ERR_TOO_LARGE;
   if (smem > 48 * 1024)
@@ -402,14 +431,61 @@ FE_EXPORT int fe_attention_general(const void* q, long long q_token_stride, long
                                    long long o_token_stride, long long o_head_stride, int dtype, const int* block_table,
                                    int max_pages, int page_size, int num_pages, int num_kv_heads, int num_q_heads,
                                    const int* positions, const int* token_entry, const float* slopes, int window,
-                                   float scale, int n_tokens, int* status, cudaStream_t stream) {
+                                   float scale, int keep_first, float softcap, float temp_coef, int temp_every,
+                                   int parts, long long q_part_stride, int k_part_stride, long long o_part_stride,
+                                   const float* gate, long long gate_stride, int out_f32, int n_tokens, int* status,
+                                   cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
-  if (num_kv_heads < 1 || num_q_heads % num_kv_heads || num_kv_heads > 65535) return FE_ERR_BAD_SHAPE;
-  if (k_dim < 1 || v_dim < 1 || k_dim > k_row || v_dim > v_row) return FE_ERR_BAD_SHAPE;
+  if (parts < 1) parts = 1;
+  if (num_kv_heads < 1 || num_q_heads % num_kv_heads || (long long)num_kv_heads * parts > 65535) return FE_ERR_BAD_SHAPE;
+  if (k_dim < 1 || v_dim < 1 || k_part_stride * (parts - 1) + k_dim > k_row || v_dim > v_row) return FE_ERR_BAD_SHAPE;
+  if (keep_first < 0 || temp_every < 0 || softcap < 0.f) return FE_ERR_BAD_SHAPE;
   GeneralAttn a{q, q_token_stride, q_head_stride, k_cache, k_row, k_dim, v_cache, v_row, v_dim, out, o_token_stride,
                 o_head_stride, block_table, max_pages, page_size, num_pages, num_kv_heads, num_q_heads, positions,
-                token_entry, slopes, window, scale};
+                token_entry, slopes, window, scale, keep_first, softcap, temp_coef, temp_every, parts, q_part_stride,
+                k_part_stride, o_part_stride, gate, gate_stride, out_f32};
   if (dtype == FE_DTYPE_F32) return dispatch_general<float>(a, n_tokens, status, stream);
   if (dtype == FE_DTYPE_BF16) return dispatch_general<bf16>(a, n_tokens, status, stream);
   return FE_ERR_BAD_DTYPE;
+}
+
+// ---------------------------------------------------------------------------
+// differential_combine: a head's two attention maps a1, a2 (32-bit, side by side:
+// [rows, 2, dv]) become o = a1 - lambda * a2, divided by its root mean square over the
+// head's dv values (eps inside the root) and multiplied by `mult`.  One warp per row
+// (token, head); everything 32-bit, one rounding on store.
+// ---------------------------------------------------------------------------
+template <typename TO>
+__global__ void __launch_bounds__(128)
+differential_combine_kernel(const float* __restrict__ maps, TO* __restrict__ out, long long rows, int dv,
+                            float lambda, float eps, float mult) {
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const float* a1 = maps + row * 2 * dv;
+  const float* a2 = a1 + dv;
+  float ss = 0.f;
+  for (int d = lane; d < dv; d += 32) {
+    const float o = a1[d] - lambda * a2[d];
+    ss = fmaf(o, o, ss);
+  }
+  const float inv = mult / sqrtf(warp_sum(ss) / (float)dv + eps);
+  for (int d = lane; d < dv; d += 32) out[row * dv + d] = from_float<TO>((a1[d] - lambda * a2[d]) * inv);
+}
+
+FE_EXPORT int fe_differential_combine(const float* maps, void* out, int out_dtype, long long rows, int dv, float lambda,
+                                      float eps, float mult, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (dv < 1) return FE_ERR_BAD_SHAPE;
+  const long long blocks = (rows + 3) / 4;
+  if (blocks > 0x7fffffffLL) return FE_ERR_TOO_LARGE;
+  int rc;
+  if (out_dtype == FE_DTYPE_F32)
+    rc = fe_launch_dependent(differential_combine_kernel<float>, dim3((unsigned)blocks), dim3(128), 0, stream, maps, (float*)out, rows, dv, lambda, eps, mult);
+  else if (out_dtype == FE_DTYPE_BF16)
+    rc = fe_launch_dependent(differential_combine_kernel<bf16>, dim3((unsigned)blocks), dim3(128), 0, stream, maps, (bf16*)out, rows, dv, lambda, eps, mult);
+  else return FE_ERR_BAD_DTYPE;
+  return rc ? rc : fe_last_error();
 }

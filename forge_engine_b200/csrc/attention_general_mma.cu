@@ -43,12 +43,21 @@ struct Params {
   const bf16* q; long long q_ts, q_hs;
   const bf16* k; int k_row;
   const bf16* v; int v_row;
-  bf16* out; long long o_ts, o_hs;
+  void* out; long long o_ts, o_hs;
   const int* table; int max_pages, page_size, num_pages, nkv, groups;
   const int* cu_tokens; const int* starts;
   const float* slopes; int window; float scale;
   int splits; int tiles; float* part;
+  // what the plain layer does not have (off when zero / null); see GeneralAttn in attention_general.cu
+  int keep_first; float softcap, temp_coef; int temp_every;
+  int parts; long long q_ps; int k_ps; long long o_ps;
+  const float* gate; long long gate_stride; int out_f32;
 };
+
+__device__ __forceinline__ float query_temperature(int pos, float coef, int every) {
+  return every > 0 ? 1.f + coef * logf((float)((pos + 1) / every + 1)) : 1.f;
+}
+__device__ __forceinline__ float sigmoidf(float x) { return 1.f / (1.f + expf(-x)); }
 
 __device__ __forceinline__ unsigned smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 
@@ -92,7 +101,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(Params p, 
   pdl_trigger();
   pdl_wait();
   const int tile = blockIdx.x / p.splits, split = blockIdx.x - tile * p.splits;
-  const int entry = blockIdx.y, kvh = blockIdx.z;
+  const int entry = blockIdx.y, kvh = blockIdx.z / p.parts, part = blockIdx.z - kvh * p.parts;
   const int t_begin = p.cu_tokens[entry];
   const int count = p.cu_tokens[entry + 1] - t_begin;
   const int start = p.starts[entry];
@@ -110,7 +119,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(Params p, 
     uint4 value = make_uint4(0, 0, 0, 0);
     if (rho < rows_total) {
       const int token = t_begin + rho / p.groups, head = kvh * p.groups + rho % p.groups;
-      value = *reinterpret_cast<const uint4*>(p.q + (size_t)token * p.q_ts + (size_t)head * p.q_hs + c * 8);
+      value = *reinterpret_cast<const uint4*>(p.q + (size_t)token * p.q_ts + (size_t)head * p.q_hs + (size_t)part * p.q_ps + c * 8);
     }
     *reinterpret_cast<uint4*>(Qs + r * KS + c * 8) = value;
   }
@@ -119,15 +128,21 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(Params p, 
   const int key_hi = start + tok_hi;                                        // last key any row sees
   const int key_lo = p.window > 0 ? max(0, start + tok_lo - p.window + 1) : 0;
   const int kt_lo = key_lo / BN, kt_hi = key_hi / BN + 1;
-  const int per = (kt_hi - kt_lo + p.splits - 1) / p.splits;
-  const int my_lo = kt_lo + split * per, my_hi = min(kt_hi, my_lo + per);
+  // keys below keep_first stay visible after the window has passed them: their tiles (those that
+  // lie before the window's first tile) are walked first; step i of the walk is key tile tile_of(i)
+  const int sink_keys = p.window > 0 ? p.keep_first : 0;
+  const int sink_tiles = min((sink_keys + BN - 1) / BN, kt_lo);
+  const int steps = sink_tiles + kt_hi - kt_lo;
+  const int per = (steps + p.splits - 1) / p.splits;
+  const int my_lo = split * per, my_hi = min(steps, my_lo + per);
+  auto tile_of = [&](int i) { return i < sink_tiles ? i : kt_lo + i - sink_tiles; };
 
   // TPR threads fetch one key row: its page is looked up once per row and tile
   constexpr int TPR = WARPS * 32 / BN;
   const int load_row = tid / TPR, load_piece = tid % TPR;
   auto load_tile = [&](int kt, int stage) {
     const int key = kt * BN + load_row;
-    bool valid = key >= key_lo && key <= key_hi;
+    bool valid = (key >= key_lo || key < sink_keys) && key <= key_hi;
     size_t row = 0;
     if (valid) {
       const int logical = key / p.page_size;
@@ -135,7 +150,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(Params p, 
       if (page < 0 || page >= p.num_pages) valid = false;     // a page the window has given back: its keys are masked anyway
       else row = ((size_t)page * p.nkv + kvh) * p.page_size + (key - logical * p.page_size);
     }
-    const bf16* ksrc = p.k + row * p.k_row;
+    const bf16* ksrc = p.k + row * p.k_row + part * p.k_ps;
     bf16* kd = Ks + stage * K_TILE + load_row * KS;
 #pragma unroll
     for (int c = load_piece; c < QC; c += TPR) cp_async16(kd + c * 8, ksrc + c * 8, valid);
@@ -150,16 +165,21 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(Params p, 
   // this thread's two rows: r_a = lane / 4 and r_a + 8 of the warp's sixteen
   const int quad = lane >> 2, pair = lane & 3;
   int row_pos[2];
-  float row_slope[2];
+  float row_slope[2], row_scale[2];
   bool row_live[2];
+  // scores are kept in units of log 2, so that exp is one exp2; with a cap the product is first
+  // brought to units of the cap, and cap * log2(e) * tanh(.) is taken
+  const bool capped = p.softcap > 0.f;
+  const float cap2 = p.softcap * LOG2E;
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int rho = row0 + rw * 16 + quad + 8 * h;
     row_live[h] = rho < rows_total;
     row_pos[h] = row_live[h] ? start + rho / p.groups : -1;
     row_slope[h] = (row_live[h] && p.slopes) ? p.slopes[kvh * p.groups + rho % p.groups] * LOG2E : 0.f;
+    const float natural = p.scale * query_temperature(max(row_pos[h], 0), p.temp_coef, p.temp_every);
+    row_scale[h] = capped ? natural / p.softcap : natural * LOG2E;
   }
-  const float scale2 = p.scale * LOG2E;       // scores are kept in units of log 2, so that exp is one exp2
   // rows of this warp, first and last position (all sixteen live), for tiles that need no mask
   const bool warp_full = row0 + rw * 16 + 15 < rows_total;
   const int warp_pos_lo = start + (row0 + rw * 16) / p.groups, warp_pos_hi = start + (row0 + rw * 16 + 15) / p.groups;
@@ -172,13 +192,14 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(Params p, 
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
   if (my_lo < my_hi) {
-    load_tile(my_lo, 0);
+    load_tile(tile_of(my_lo), 0);
     cp_commit();
   }
-  for (int kt = my_lo; kt < my_hi; ++kt) {
-    const int stage = (kt - my_lo) & 1;
-    if (kt + 1 < my_hi) {
-      load_tile(kt + 1, stage ^ 1);
+  for (int step = my_lo; step < my_hi; ++step) {
+    const int kt = tile_of(step);
+    const int stage = (step - my_lo) & 1;
+    if (step + 1 < my_hi) {
+      load_tile(tile_of(step + 1), stage ^ 1);
       cp_commit();
       cp_wait<1>();
     } else {
@@ -222,7 +243,9 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(Params p, 
         for (int c = 0; c < 4; ++c) {
           const int h = c >> 1;
           const int key = kt * BN + j * 8 + pair * 2 + (c & 1);
-          const float sc = s[j][c] * scale2 - row_slope[h] * (float)(row_pos[h] - key);
+          float sc = s[j][c] * row_scale[h];
+          if (capped) sc = cap2 * tanhf(sc);
+          sc -= row_slope[h] * (float)(row_pos[h] - key);
           s[j][c] = sc;
           mx[h] = fmaxf(mx[h], sc);
         }
@@ -234,8 +257,11 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(Params p, 
         for (int c = 0; c < 4; ++c) {
           const int h = c >> 1;
           const int key = kt * BN + j * 8 + pair * 2 + (c & 1);
-          const bool visible = row_live[h] && key <= row_pos[h] && (p.window <= 0 || key > row_pos[h] - p.window);
-          const float sc = visible ? s[j][c] * scale2 - row_slope[h] * (float)(row_pos[h] - key) : -INFINITY;
+          const bool visible = row_live[h] && key <= row_pos[h] &&
+                               (p.window <= 0 || key > row_pos[h] - p.window || key < sink_keys);
+          float sc = s[j][c] * row_scale[h];
+          if (capped) sc = cap2 * tanhf(sc);
+          sc = visible ? sc - row_slope[h] * (float)(row_pos[h] - key) : -INFINITY;
           s[j][c] = sc;
           mx[h] = fmaxf(mx[h], sc);
         }
@@ -299,17 +325,26 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(Params p, 
       if (!row_live[h]) continue;
       const int rho = row0 + rw * 16 + quad + 8 * h;
       const int token = t_begin + rho / p.groups, head = kvh * p.groups + rho % p.groups;
-      bf16* dst = p.out + (size_t)token * p.o_ts + (size_t)head * p.o_hs;
-      const float inv = l_run[h] > 0.f ? 1.f / l_run[h] : 0.f;
+      const size_t at = (size_t)token * p.o_ts + (size_t)head * p.o_hs + (size_t)part * p.o_ps;
+      float inv = l_run[h] > 0.f ? 1.f / l_run[h] : 0.f;
+      if (p.gate) inv *= sigmoidf(p.gate[(size_t)token * p.gate_stride + head]);
+      if (p.out_f32) {
+        float* dst = reinterpret_cast<float*>(p.out) + at;
 #pragma unroll
-      for (int n = 0; n < DVW / 8; ++n)
-        *reinterpret_cast<__nv_bfloat162*>(dst + vcol0 + n * 8 + pair * 2) =
-            __floats2bfloat162_rn(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);
+        for (int n = 0; n < DVW / 8; ++n)
+          *reinterpret_cast<float2*>(dst + vcol0 + n * 8 + pair * 2) = make_float2(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);
+      } else {
+        bf16* dst = reinterpret_cast<bf16*>(p.out) + at;
+#pragma unroll
+        for (int n = 0; n < DVW / 8; ++n)
+          *reinterpret_cast<__nv_bfloat162*>(dst + vcol0 + n * 8 + pair * 2) =
+              __floats2bfloat162_rn(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);
+      }
     }
     return;
   }
-  // partial result of this split: [entry][tile][kvh][split][row][DV + 2]
-  float* mine = p.part + ((((size_t)entry * p.tiles + tile) * p.nkv + kvh) * p.splits + split) * (size_t)BM * (DV + 2);
+  // partial result of this split: [entry][tile][kvh, part][split][row][DV + 2]
+  float* mine = p.part + ((((size_t)entry * p.tiles + tile) * (p.nkv * p.parts) + blockIdx.z) * p.splits + split) * (size_t)BM * (DV + 2);
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int r = rw * 16 + quad + 8 * h;
@@ -336,12 +371,12 @@ __global__ void __launch_bounds__(128) attention_mma_merge_kernel(Params p) {
   pdl_trigger();
   pdl_wait();
   const int tile = blockIdx.x / (BM / MERGE_ROWS), piece = blockIdx.x % (BM / MERGE_ROWS);
-  const int entry = blockIdx.y, kvh = blockIdx.z;
+  const int entry = blockIdx.y, kvh = blockIdx.z / p.parts, part = blockIdx.z - kvh * p.parts;
   const int t_begin = p.cu_tokens[entry];
   const int rows_total = (p.cu_tokens[entry + 1] - t_begin) * p.groups;
   const int first = tile * BM + piece * MERGE_ROWS;
   if (first >= rows_total) return;
-  const float* base = p.part + (((size_t)entry * p.tiles + tile) * p.nkv + kvh) * p.splits * (size_t)BM * (DV + 2);
+  const float* base = p.part + (((size_t)entry * p.tiles + tile) * (p.nkv * p.parts) + blockIdx.z) * p.splits * (size_t)BM * (DV + 2);
   const int rows = min(MERGE_ROWS, rows_total - first);
   {
     // a warp per row, a lane per split: maxima and normalisers are fetched side by side
@@ -366,14 +401,18 @@ __global__ void __launch_bounds__(128) attention_mma_merge_kernel(Params p) {
     for (int s = 0; s < p.splits; ++s) num = fmaf(base[((size_t)s * BM + r) * (DV + 2) + d], weight[lr][s], num);
     const int rho = tile * BM + r;
     const int token = t_begin + rho / p.groups, head = kvh * p.groups + rho % p.groups;
-    p.out[(size_t)token * p.o_ts + (size_t)head * p.o_hs + d] = __float2bfloat16_rn(num * inverse[lr]);
+    float value = num * inverse[lr];
+    if (p.gate) value *= sigmoidf(p.gate[(size_t)token * p.gate_stride + head]);
+    const size_t at = (size_t)token * p.o_ts + (size_t)head * p.o_hs + (size_t)part * p.o_ps + d;
+    if (p.out_f32) reinterpret_cast<float*>(p.out)[at] = value;
+    else reinterpret_cast<bf16*>(p.out)[at] = __float2bfloat16_rn(value);
   }
 }
 
 }  // namespace
 
 // Floats of workspace a launch with these sizes needs (0 for one split).
-FE_EXPORT long long GM_NAME(fe_attention_gmma_workspace_)(int entries, int max_new, int groups, int nkv, int splits) {
+FE_EXPORT long long GM_NAME(fe_attention_gmma_workspace_)(int entries, int max_new, int groups, int nkv /* times parts */, int splits) {
   if (splits <= 1) return 0;
   const long long tiles = ((long long)max_new * groups + BM - 1) / BM;
   return (long long)entries * tiles * nkv * splits * BM * (DV + 2);
@@ -384,30 +423,36 @@ FE_EXPORT int GM_NAME(fe_attention_gmma_)(const void* q, long long q_ts, long lo
                                           const int* block_table, int max_pages, int page_size, int num_pages, int nkv,
                                           int num_q_heads, const int* cu_tokens, const int* starts, int entries,
                                           int max_new, const float* slopes, int window, float scale, int splits,
-                                          float* workspace, int* status, cudaStream_t stream) {
+                                          float* workspace, int keep_first, float softcap, float temp_coef,
+                                          int temp_every, int parts, long long q_ps, int k_ps, long long o_ps,
+                                          const float* gate, long long gate_stride, int out_f32, int* status,
+                                          cudaStream_t stream) {
   if (entries <= 0 || max_new <= 0) return 0;
-  if (nkv < 1 || num_q_heads % nkv || nkv > 65535 || entries > 65535) return FE_ERR_BAD_SHAPE;
-  if (k_row % 8 || v_row % 8 || q_ts % 8 || q_hs % 8 || o_ts % 2 || o_hs % 2) return FE_ERR_BAD_ALIGN;
+  if (parts < 1) parts = 1;
+  if (nkv < 1 || num_q_heads % nkv || (long long)nkv * parts > 65535 || entries > 65535) return FE_ERR_BAD_SHAPE;
+  if (keep_first < 0 || temp_every < 0 || softcap < 0.f || k_ps * (parts - 1) + DK > k_row) return FE_ERR_BAD_SHAPE;
+  if (k_row % 8 || v_row % 8 || q_ts % 8 || q_hs % 8 || o_ts % 2 || o_hs % 2 || q_ps % 8 || k_ps % 8 || o_ps % 2) return FE_ERR_BAD_ALIGN;
   if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) % 16 || (uintptr_t)out % 4) return FE_ERR_BAD_ALIGN;
   if (splits < 1) splits = 1;
   if (splits > MAX_SPLITS) return FE_ERR_BAD_SHAPE;
   if (splits > 1 && workspace == nullptr) return FE_ERR_BAD_SHAPE;
   const int groups = num_q_heads / nkv;
   const int tiles = (int)(((long long)max_new * groups + BM - 1) / BM);
-  Params p{(const bf16*)q, q_ts, q_hs, (const bf16*)k_cache, k_row, (const bf16*)v_cache, v_row, (bf16*)out, o_ts, o_hs,
+  Params p{(const bf16*)q, q_ts, q_hs, (const bf16*)k_cache, k_row, (const bf16*)v_cache, v_row, out, o_ts, o_hs,
            block_table, max_pages, page_size, num_pages, nkv, groups, cu_tokens, starts, slopes, window, scale,
-           splits, tiles, workspace};
+           splits, tiles, workspace, keep_first, softcap, temp_coef, temp_every, parts, q_ps, k_ps, o_ps, gate,
+           gate_stride, out_f32};
   static bool configured = false;
   if (!configured) {
     const cudaError_t rc = cudaFuncSetAttribute(attention_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
     if (rc != cudaSuccess) return (int)rc;
     configured = true;
   }
-  dim3 grid((unsigned)tiles * splits, entries, nkv);
+  dim3 grid((unsigned)tiles * splits, entries, nkv * parts);
   int rc = fe_launch_dependent(attention_mma_kernel, grid, dim3(WARPS * 32), SMEM_BYTES, stream, p, status);
   if (rc) return rc;
   if (splits > 1) {
-    rc = fe_launch_dependent(attention_mma_merge_kernel, dim3(tiles * (BM / MERGE_ROWS), entries, nkv), dim3(128), 0, stream, p);
+    rc = fe_launch_dependent(attention_mma_merge_kernel, dim3(tiles * (BM / MERGE_ROWS), entries, nkv * parts), dim3(128), 0, stream, p);
     if (rc) return rc;
   }
   return fe_last_error();

@@ -46,14 +46,14 @@ FE_EXPORT int fe_embedding(const int* ids, const void* table, int table_dtype, f
 }
 
 // ---------------------------------------------------------------------------
-// x = residual[src] + update[src];  residual[src] = x (optional);
+// x = residual[src] + update[src] (+ shift, one vector for all rows);  residual[src] = x (optional);
 // out[r] = x * rsqrt(mean(x^2) + eps) * weight       -- all in 32-bit, one rounding
 // src = row_map ? row_map[r] : r
 // ---------------------------------------------------------------------------
 template <typename TU, typename TO, int PER>
 __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TU* __restrict__ update,
                                    const float* __restrict__ weight, TO* __restrict__ out,
-                                   const int* __restrict__ row_map, int size, float eps,
+                                   const int* __restrict__ row_map, const float* __restrict__ shift, int size, float eps,
                                    int write_residual) {
   // PER > 0: every thread keeps its PER elements (strided by blockDim) in registers between
   // the two passes; PER == 0: rows too long for that are read twice.
@@ -75,6 +75,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TU* __res
       if (i < size) {
         x[j] = res[i];
         if (upd) x[j] += to_float(upd[i]);
+        if (shift) x[j] += shift[i];
         if (write_residual) res[i] = x[j];
         ss += x[j] * x[j];
       }
@@ -89,6 +90,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TU* __res
     for (int i = threadIdx.x; i < size; i += blockDim.x) {
       float x = res[i];
       if (upd) x += to_float(upd[i]);
+      if (shift) x += shift[i];
       if (write_residual) res[i] = x;
       ss += x * x;
     }
@@ -97,6 +99,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TU* __res
     for (int i = threadIdx.x; i < size; i += blockDim.x) {
       float x = res[i];
       if (upd && !write_residual) x += to_float(upd[i]);
+      if (shift && !write_residual) x += shift[i];
       dst[i] = from_float<TO>(x * inv * weight[i]);
     }
   }
@@ -107,7 +110,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TU* __res
 template <typename TU, typename TO, int PER>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const TU* __restrict__ update,
                                        const float* __restrict__ weight, TO* __restrict__ out,
-                                       const int* __restrict__ row_map, int size, float eps,
+                                       const int* __restrict__ row_map, const float* __restrict__ shift, int size, float eps,
                                        int write_residual) {
   __shared__ float scratch[33];
   pdl_trigger();
@@ -128,6 +131,12 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const TU* _
       if (upd) {
         float u[4];
         load4(upd + 4 * g, u);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) x[j][e] += u[e];
+      }
+      if (shift) {
+        float u[4];
+        load4(shift + 4 * g, u);
 #pragma unroll
         for (int e = 0; e < 4; ++e) x[j][e] += u[e];
       }
@@ -152,13 +161,13 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const TU* _
 
 FE_EXPORT int fe_add_rmsnorm(float* residual, const void* update, int update_dtype,
                              const float* weight, void* out, int out_dtype, const int* row_map,
-                             int rows, int size, float eps, int write_residual,
+                             const float* shift, int rows, int size, float eps, int write_residual,
                              cudaStream_t stream) {
   if (rows <= 0) return 0;
   int rc = 0;
   const int update_bytes = update_dtype == FE_DTYPE_F32 ? 16 : 8, out_bytes = out_dtype == FE_DTYPE_F32 ? 16 : 8;
   if ((size % 4) == 0 && size <= 16384 && ((uintptr_t)residual % 16) == 0 && ((uintptr_t)weight % 16) == 0 &&
-      ((uintptr_t)update % update_bytes) == 0 && ((uintptr_t)out % out_bytes) == 0) {
+      ((uintptr_t)update % update_bytes) == 0 && ((uintptr_t)out % out_bytes) == 0 && ((uintptr_t)shift % 16) == 0) {
     const int groups = size / 4;
     const int per = groups <= 1024 ? 1 : groups <= 2048 ? 2 : 4;
     const int vthreads = (((groups + per - 1) / per) + 31) / 32 * 32;
@@ -166,13 +175,13 @@ FE_EXPORT int fe_add_rmsnorm(float* residual, const void* update, int update_dty
     do {                                                                                                          \
       if (per == 1)                                                                                               \
         rc = fe_launch_dependent(add_rmsnorm_vec_kernel<TU, TO, 1>, dim3(rows), dim3(vthreads), 0, stream, residual, \
-            (const TU*)update, weight, (TO*)out, row_map, size, eps, write_residual);                             \
+            (const TU*)update, weight, (TO*)out, row_map, shift, size, eps, write_residual);                             \
       else if (per == 2)                                                                                          \
         rc = fe_launch_dependent(add_rmsnorm_vec_kernel<TU, TO, 2>, dim3(rows), dim3(vthreads), 0, stream, residual, \
-            (const TU*)update, weight, (TO*)out, row_map, size, eps, write_residual);                             \
+            (const TU*)update, weight, (TO*)out, row_map, shift, size, eps, write_residual);                             \
       else                                                                                                        \
         rc = fe_launch_dependent(add_rmsnorm_vec_kernel<TU, TO, 4>, dim3(rows), dim3(vthreads), 0, stream, residual, \
-            (const TU*)update, weight, (TO*)out, row_map, size, eps, write_residual);                             \
+            (const TU*)update, weight, (TO*)out, row_map, shift, size, eps, write_residual);                             \
     } while (0)
     if (update_dtype == FE_DTYPE_F32 && out_dtype == FE_DTYPE_F32) LAUNCH_VEC(float, float);
     else if (update_dtype == FE_DTYPE_BF16 && out_dtype == FE_DTYPE_BF16) LAUNCH_VEC(bf16, bf16);
@@ -189,13 +198,13 @@ FE_EXPORT int fe_add_rmsnorm(float* residual, const void* update, int update_dty
   do {                                                                                               \
     if (per <= 4)                                                                                    \
       rc = fe_launch_dependent(add_rmsnorm_kernel<TU, TO, 4>, dim3(rows), dim3(threads), 0, stream, residual, (const TU*)update,      \
-          weight, (TO*)out, row_map, size, eps, write_residual);                                     \
+          weight, (TO*)out, row_map, shift, size, eps, write_residual);                                     \
     else if (per <= 16)                                                                              \
       rc = fe_launch_dependent(add_rmsnorm_kernel<TU, TO, 16>, dim3(rows), dim3(threads), 0, stream, residual, (const TU*)update,     \
-          weight, (TO*)out, row_map, size, eps, write_residual);                                     \
+          weight, (TO*)out, row_map, shift, size, eps, write_residual);                                     \
     else                                                                                             \
       rc = fe_launch_dependent(add_rmsnorm_kernel<TU, TO, 0>, dim3(rows), dim3(threads), 0, stream, residual, (const TU*)update,      \
-          weight, (TO*)out, row_map, size, eps, write_residual);                                     \
+          weight, (TO*)out, row_map, shift, size, eps, write_residual);                                     \
   } while (0)
   if (update_dtype == FE_DTYPE_F32 && out_dtype == FE_DTYPE_F32) LAUNCH(float, float);
   else if (update_dtype == FE_DTYPE_BF16 && out_dtype == FE_DTYPE_BF16) LAUNCH(bf16, bf16);

@@ -221,12 +221,20 @@ FE_EXPORT int fe_stream_mix_norm(float* streams, int n_streams, const void* upda
 }
 
 // ---------------------------------------------------------------------------
-// out[n, i] = act(gate_up[n, i]) * gate_up[n, inter + i];  act 0: SiLU, 1: the tanh form of GELU
+// out[n, i] = act(gate_up[n, i]) * gate_up[n, inter + i];  act 0: SiLU, 1: the tanh form of GELU,
+// 2: the clamped unit g' sigmoid(slope g') (u' + 1) with g' = min(g, limit), u' = clamp(u, +-limit)
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ float act_apply(float z, int act) {
-  if (act == 0) return z / (1.f + expf(-z));
+struct ActParams { int act; float limit, slope; };
+
+__device__ __forceinline__ float act_apply(float z, float u, const ActParams& a) {
+  if (a.act == 0) return z / (1.f + expf(-z)) * u;
+  if (a.act == 2) {
+    const float g = fminf(z, a.limit);
+    const float v = fminf(fmaxf(u, -a.limit), a.limit);
+    return g / (1.f + expf(-a.slope * g)) * (v + 1.f);
+  }
   const float inner = 0.7978845608028654f * (z + 0.044715f * z * z * z);
-  return 0.5f * z * (1.f + tanhf(inner));
+  return 0.5f * z * (1.f + tanhf(inner)) * u;
 }
 
 // block == 0: a row is [all gate | all up]; block == B > 0: it alternates B gate features, B up
@@ -237,7 +245,7 @@ __device__ __forceinline__ void gate_up_at(int i, int inter, int block, int* gat
 }
 
 template <typename TI, typename TO>
-__global__ void act_mul_kernel(const TI* __restrict__ gate_up, TO* __restrict__ out, int inter, int act, int block) {
+__global__ void act_mul_kernel(const TI* __restrict__ gate_up, TO* __restrict__ out, int inter, ActParams act, int block) {
   pdl_trigger();
   pdl_wait();
   const int row = blockIdx.x;
@@ -246,12 +254,12 @@ __global__ void act_mul_kernel(const TI* __restrict__ gate_up, TO* __restrict__ 
   for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < inter; i += gridDim.y * blockDim.x) {
     int ga, ua;
     gate_up_at(i, inter, block, &ga, &ua);
-    o[i] = from_float<TO>(act_apply(to_float(g[ga]), act) * to_float(g[ua]));
+    o[i] = from_float<TO>(act_apply(to_float(g[ga]), to_float(g[ua]), act));
   }
 }
 
 template <typename TI, typename TO>
-__global__ void act_mul_vec_kernel(const TI* __restrict__ gate_up, TO* __restrict__ out, int inter, int act, int block) {
+__global__ void act_mul_vec_kernel(const TI* __restrict__ gate_up, TO* __restrict__ out, int inter, ActParams act, int block) {
   pdl_trigger();
   pdl_wait();
   const int row = blockIdx.x;
@@ -264,15 +272,16 @@ __global__ void act_mul_vec_kernel(const TI* __restrict__ gate_up, TO* __restric
     load4(g + ga, a);
     load4(g + ua, b);
 #pragma unroll
-    for (int e = 0; e < 4; ++e) a[e] = act_apply(a[e], act) * b[e];
+    for (int e = 0; e < 4; ++e) a[e] = act_apply(a[e], b[e], act);
     store4(o + i, a);
   }
 }
 
-FE_EXPORT int fe_act_mul(const void* gate_up, int in_dtype, void* out, int out_dtype, int rows, int inter, int act,
-                         int block, cudaStream_t stream) {
+FE_EXPORT int fe_act_mul(const void* gate_up, int in_dtype, void* out, int out_dtype, int rows, int inter, int act_kind,
+                         int block, float limit, float slope, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  if (act != 0 && act != 1) return FE_ERR_BAD_SHAPE;
+  if (act_kind < 0 || act_kind > 2) return FE_ERR_BAD_SHAPE;
+  const ActParams act{act_kind, limit, slope};
   if (block < 0 || (block > 0 && (inter % block) != 0)) return FE_ERR_BAD_SHAPE;
   const int threads = 256;
   if ((inter % 4) == 0 && (block % 4) == 0 && ((uintptr_t)gate_up % 16) == 0 && ((uintptr_t)out % 16) == 0) {

@@ -34,6 +34,8 @@ def expected_tensors(spec: ModelSpec) -> dict:
             prefix = layer.names[role]
             for local, info in shapes.items():
                 out[join_name(prefix, local)] = info
+    for name, shape, role in getattr(spec, "extra_tensors", ()):
+        out[name] = WeightInfo(tuple(shape), role)
     if not spec.tie_embeddings:
         out[spec.head_name] = WeightInfo((spec.vocab_size, spec.hidden_size))
     return out
@@ -75,6 +77,13 @@ class DecoderModel:
         norm_shapes = part_class(spec.final_norm).weight_shapes(spec.final_norm)
         self.final_norm = build_part(spec.final_norm, _Scoped(weights, spec.final_norm_name, norm_shapes), ctx)
         self.head = Linear(self.embed if spec.tie_embeddings else weights[spec.head_name], status=ctx.status)
+        # vectors that runs add to the residual stream before they start, kept in 32-bit
+        self.shifts: dict = {}
+        for run in spec.schedule:
+            shift = getattr(run, "shift", None)
+            if shift is not None and shift not in self.shifts:
+                name, row = shift
+                self.shifts[shift] = weights[name][row].to(device=ctx.device, dtype=torch.float32).contiguous()
         for index, run in enumerate(spec.schedule):
             if not 0 <= run.layer < len(self.blocks):
                 raise ValueError(f"run {index} names layer {run.layer}, which does not exist")
@@ -146,7 +155,11 @@ class DecoderModel:
                              scale=getattr(self.spec, "embedding_scale", 1.0))
         pending = None
         for index, run in enumerate(self.spec.schedule):
-            pending = self.blocks[run.layer].forward(h, pending, batch, cache.view(index))
+            shift = getattr(run, "shift", None)
+            if shift is None:
+                pending = self.blocks[run.layer].forward(h, pending, batch, cache.view(index))
+            else:
+                pending = self.blocks[run.layer].forward(h, pending, batch, cache.view(index), shift=self.shifts[shift])
         if batch.n_want == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.ctx.device)
         # an arrangement whose pending update is more than a tensor folds it into the final norm itself

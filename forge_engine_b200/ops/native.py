@@ -58,16 +58,22 @@ def _declare(handle: ctypes.CDLL) -> None:
     signatures = {
         "fe_embedding": [p, p, i, p, i, i, i, f, i, p, p],
         "fe_stream_mix_norm": [p, i, p, i, f, p, p, p, i, p, f, p, i, p, i, i, i, p],
-        "fe_act_mul": [p, i, p, i, i, i, i, i, p],
+        "fe_act_mul": [p, i, p, i, i, i, i, i, f, f, p],
         "fe_gated_rmsnorm": [p, p, i, i, p, p, i, i, i, f, p],
         "fe_qkv_prepare": [p, i, i, i, i, i, i, p, i, p, i, i, i, i, i, p, i, p, i, i, i, f, p, i, i, p, ll, ll, i,
                            p, p, i, p, i, i, i, p, p, i, p, p],
-        "fe_attention_general": [p, ll, ll, p, i, i, p, i, i, p, ll, ll, i, p, i, i, i, i, i, p, p, p, i, f, i, p, p],
+        "fe_attention_general": [p, ll, ll, p, i, i, p, i, i, p, ll, ll, i, p, i, i, i, i, i, p, p, p, i, f,
+                                 i, f, f, i, i, ll, i, ll, p, ll, i, i, p, p],
+        "fe_differential_combine": [p, p, i, ll, i, f, f, f, p],
+        "fe_moe_route": [p, ll, i, i, i, i, i, p, p, p, p, p, p, p, p, p, i, p],
+        "fe_moe_grouped": [p, i, ll, p, p, i, p, i, i, i, i, i, p, p, p, p, p, i, f, f, i, p],
+        "fe_moe_combine": [p, p, p, i, i, p, i, p, ll, p, i, i, p],
+        "fe_moe_max_tiles": [i, i],
         "fe_linear_recurrence": [p, i, i, i, i, i, i, p, p, p, p, p, i, i, i, i, i, p],
         "fe_linear_recurrence_chunked": [p, i, i, i, i, i, i, p, p, p, p, p, p, i, i, i, i, i, i, p],
         "fe_linear_recurrence_chunks": [i, i],
         "fe_gemm_simt_batched": [p, i, p, i, p, i, i, i, i, i, ll, ll, ll, ll, ll, p],
-        "fe_add_rmsnorm": [p, p, i, p, p, i, p, i, i, f, i, p],
+        "fe_add_rmsnorm": [p, p, i, p, p, i, p, p, i, i, f, i, p],
         "fe_silu_mul": [p, p, i, i, i, i, p],
         "fe_qk_rope_cache": [p, i, p, p, f, p, p, i, p, p, p, p, p, i, i, i, i, i, i, i, i, p, p],
         "fe_qk_rope_cache_sums": [p, p, p, p, f, p, p, p, p, p, p, p, i, i, i, i, i, i, i, i, p, p],
@@ -300,18 +306,97 @@ def stream_mix_norm(
     )
 
 
-ACT_SILU, ACT_GELU_TANH = 0, 1
+ACT_SILU, ACT_GELU_TANH, ACT_CLAMPED_SWISH = 0, 1, 2
 
 
-def act_mul(gate_up: torch.Tensor, out: torch.Tensor, act: int, block: int = 0) -> None:
-    """out[n, i] = act(gate) * up in 32-bit, rounded on store.  ``block`` 0: a row of
-    ``gate_up`` is all gate features then all up features; ``block`` B: it alternates B gate,
-    B up features."""
+def act_mul(gate_up: torch.Tensor, out: torch.Tensor, act: int, block: int = 0, limit: float = 0.0,
+            slope: float = 1.0) -> None:
+    """out[n, i] = act(gate) * up in 32-bit, rounded on store; for ACT_CLAMPED_SWISH
+    g' sigmoid(slope g') (u' + 1) with g' = min(gate, limit), u' = clamp(up, -limit, limit).
+    ``block`` 0: a row of ``gate_up`` is all gate features then all up features; ``block`` B:
+    it alternates B gate, B up features."""
     _dense(gate_up, "gate_up"), _dense(out, "out")
     rows, inter = out.shape
     assert gate_up.shape == (rows, 2 * inter)
-    check(lib().fe_act_mul(ptr(gate_up), code(gate_up), ptr(out), code(out), rows, inter, int(act), int(block), stream()),
-          "act_mul")
+    check(lib().fe_act_mul(ptr(gate_up), code(gate_up), ptr(out), code(out), rows, inter, int(act), int(block),
+                           float(limit), float(slope), stream()), "act_mul")
+
+
+def differential_combine(maps: torch.Tensor, out: torch.Tensor, value_dim: int, lam: float, eps: float, mult: float) -> None:
+    """``maps`` 32-bit [N, heads * 2 * value_dim] holds two attention maps per head side by
+    side; out[N, heads * value_dim] = (a1 - lam a2) / sqrt(mean((a1 - lam a2)^2) + eps) * mult
+    per head, in 32-bit, rounded on store."""
+    _dense(maps, "maps"), _dense(out, "out")
+    assert maps.dtype == torch.float32 and maps.numel() == 2 * out.numel() and out.numel() % value_dim == 0
+    check(lib().fe_differential_combine(ptr(maps), ptr(out), code(out), out.numel() // value_dim, int(value_dim),
+                                        float(lam), float(eps), float(mult), stream()), "differential_combine")
+
+
+def moe_max_tiles(slots: int, experts: int) -> int:
+    """Row tiles the grouped products are launched with for ``slots`` (token, choice) pairs."""
+    return int(lib().fe_moe_max_tiles(int(slots), int(experts)))
+
+
+def moe_route(logits: torch.Tensor, experts: int, top: int, softmax: bool, renormalise: bool, counts: torch.Tensor,
+              ints: torch.Tensor, slot_weight: torch.Tensor, max_tiles: int) -> dict:
+    """Choose ``top`` of ``experts`` per token from 32-bit ``logits`` [N, >= experts] and lay
+    the (token, choice) slots out by expert.  ``counts`` int32 [experts] must be zero (it is
+    zero again afterwards); ``ints`` is int32 scratch of at least 4 * N * top + experts + 1 +
+    2 * max_tiles elements.  Returns views of it by name."""
+    n = logits.shape[0]
+    slots = n * top
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and logits.shape[1] >= experts
+    assert counts.dtype == torch.int32 and counts.numel() >= experts and ints.dtype == torch.int32
+    assert slot_weight.dtype == torch.float32 and slot_weight.numel() >= slots
+    assert ints.numel() >= 4 * slots + experts + 1 + 2 * max_tiles
+    names = (("slot_expert", slots), ("slot_rank", slots), ("slot_row", slots), ("row_slot", slots),
+             ("offsets", experts + 1), ("tile_expert", max_tiles), ("tile_row", max_tiles))
+    views, at = {}, 0
+    for name, count in names:
+        views[name] = ints[at : at + count]
+        at += count
+    check(lib().fe_moe_route(ptr(logits), int(logits.stride(0)) if n > 1 else int(logits.shape[1]), n, int(experts),
+                             int(top), 1 if softmax else 0, 1 if renormalise else 0, ptr(counts),
+                             ptr(views["slot_expert"]), ptr(slot_weight), ptr(views["slot_rank"]), ptr(views["slot_row"]),
+                             ptr(views["row_slot"]), ptr(views["offsets"]), ptr(views["tile_expert"]),
+                             ptr(views["tile_row"]), int(max_tiles), stream()), "moe_route")
+    global LAUNCHES
+    LAUNCHES += 1
+    return views
+
+
+def moe_grouped(a: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor | None, out: torch.Tensor, plan: dict, top: int,
+                max_tiles: int, *, gather: bool, slot_weight: torch.Tensor | None = None, act: int = 0,
+                limit: float = 0.0, slope: float = 1.0) -> None:
+    """One product over rows grouped by expert.  ``w1`` (and ``w2``) [experts, n, k];
+    ``gather``: ``a`` holds the tokens' activations [N, k] and a sorted row reads its slot's
+    token, times ``slot_weight`` when given; else ``a`` holds sorted rows [slots, k].  With
+    ``w2``: out = act(a w1^T, a w2^T) (see ``act_mul``), else out = a w1^T."""
+    _dense(a, "a"), _dense(w1, "w1"), _dense(out, "out")
+    experts, n, k = w1.shape
+    assert a.shape[1] == k and out.shape[1] == n and (w2 is None or (w2.shape == w1.shape and w2.dtype == w1.dtype))
+    use_mma = (a.dtype == torch.bfloat16 and w1.dtype == torch.bfloat16 and k % 8 == 0
+               and _os.environ.get("FORGE_ENGINE_MOE_MMA", "1") != "0")
+    check(lib().fe_moe_grouped(ptr(a), code(a), int(k), ptr(w1), ptr(w2), code(w1), ptr(out), code(out), int(n), int(k),
+                               int(top), int(max_tiles), ptr(plan["offsets"]), ptr(plan["tile_expert"]),
+                               ptr(plan["tile_row"]), ptr(plan["row_slot"]) if gather else None,
+                               ptr(slot_weight) if gather else None, int(act), float(limit), float(slope),
+                               1 if use_mma else 0, stream()), "moe_grouped")
+
+
+def moe_combine(rows: torch.Tensor, plan: dict, top: int, out: torch.Tensor, *, slot_weight: torch.Tensor | None = None,
+                shared: torch.Tensor | None = None, shared_logit: torch.Tensor | None = None) -> None:
+    """out[token] = sum over the token's slots of rows[slot's row] (times ``slot_weight``) +
+    sigmoid(shared_logit[token]) * shared[token] (the gate 1 without a logit); 32-bit sums."""
+    _dense(rows, "rows"), _dense(out, "out")
+    n, width = out.shape
+    assert rows.dtype == torch.float32 and rows.shape == (n * top, width)
+    assert shared is None or (shared.shape == out.shape and shared.is_contiguous())
+    assert shared_logit is None or (shared_logit.dtype == torch.float32 and shared_logit.shape[0] == n)
+    check(lib().fe_moe_combine(ptr(rows), ptr(plan["slot_row"]), ptr(slot_weight), int(top), int(width), ptr(shared),
+                               code(shared) if shared is not None else F32, ptr(shared_logit),
+                               int(shared_logit.stride(0)) if shared_logit is not None and n > 1 else 1,
+                               ptr(out), code(out), n, stream()), "moe_combine")
 
 
 def gated_rmsnorm(x: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float) -> None:
@@ -420,7 +505,8 @@ def general_attention_lib(key_dim: int, value_dim: int, value_in_key: bool):
         suffix = f"{key_dim}_{value_dim}_{1 if value_in_key else 0}"
         run = getattr(handle, f"fe_attention_gmma_{suffix}")
         p, i, f, ll = c_void_p, c_int, c_float, ctypes.c_longlong
-        run.argtypes = [p, ll, ll, p, i, p, i, p, ll, ll, p, i, i, i, i, i, p, p, i, i, p, i, f, i, p, p, p]
+        run.argtypes = [p, ll, ll, p, i, p, i, p, ll, ll, p, i, i, i, i, i, p, p, i, i, p, i, f, i, p,
+                        i, f, f, i, i, ll, i, ll, p, ll, i, p, p]
         run.restype = c_int
         space = getattr(handle, f"fe_attention_gmma_workspace_{suffix}")
         space.argtypes = [i, i, i, i, i]
@@ -437,7 +523,8 @@ def general_mma_takes(dtype, key_dim: int, value_dim: int) -> bool:
             and _os.environ.get("FORGE_ENGINE_GENERAL_MMA", "1") != "0")
 
 
-def general_splits(entries: list, groups: int, kv_heads: int, window: int | None, slots: int = 296) -> int:
+def general_splits(entries: list, groups: int, kv_heads: int, window: int | None, slots: int = 296,
+                   keep_first: int = 0) -> int:
     """How many blocks share the keys of one row tile, for a step of ``entries`` ((slot,
     cached, new) each).  Only steps whose entries all fit one row tile (decoding, short
     portions) are split: enough blocks to fill the GPU once, each with at least two key
@@ -446,7 +533,7 @@ def general_splits(entries: list, groups: int, kv_heads: int, window: int | None
         return 1
     longest = max(start + count for _, start, count in entries)
     if window:
-        longest = min(longest, window + max(count for _, _, count in entries))
+        longest = min(longest, window + max(count for _, _, count in entries) + int(keep_first or 0))
     tiles = -(-longest // 64)
     wish = min(slots // max(1, len(entries) * kv_heads), tiles // 2, 32)
     return 1 if wish < 2 else 1 << (wish.bit_length() - 1)
@@ -471,6 +558,12 @@ def attention_general(
     status: torch.Tensor,
     entries: tuple | None = None,
     splits: int = 1,
+    keep_first: int = 0,
+    softcap: float | None = None,
+    query_temperature: tuple | None = None,
+    parts: int = 1,
+    part_strides: tuple = (0, 0, 0),
+    gate: torch.Tensor | None = None,
 ) -> None:
     """Paged causal attention for any key and value size: scores, softmax and sums in 32-bit.
 
@@ -483,25 +576,41 @@ def attention_general(
     is the first ``k_dim`` elements of a row, the value the first ``v_dim`` of ``v_cache``'s
     row (``v_cache`` may be ``k_cache`` itself: one cached vector that is key and value).
     ``slopes`` (per query head, 32-bit) takes slope * (query position - key position) off
-    every score; ``window`` keeps the query's own and the window - 1 keys before it."""
+    every score; ``window`` keeps the query's own and the window - 1 keys before it, and with
+    ``keep_first`` the keys at positions below it as well.  ``softcap`` c: scores become
+    c tanh(score / c); ``query_temperature`` (coef, every): a query at position p has its
+    scores multiplied by 1 + coef ln(floor((p + 1) / every) + 1).  ``parts`` > 1: every head has
+    that many score maps over the same values; map m reads its query ``part_strides[0]`` * m
+    elements after the head's first, its key ``part_strides[1]`` * m elements into the cached
+    row, and writes ``part_strides[2]`` * m elements after the head's first output.  ``gate``
+    (32-bit [N, >= heads], a column slice is fine): row (token, head) is multiplied by
+    sigmoid(gate[token, head]).  ``out`` may be 32-bit whatever the cache holds."""
     num_pages, nkv, page_size, k_row = k_cache.shape
     v_row = v_cache.shape[3]
     n = positions.numel()
-    assert q.dtype == k_cache.dtype == v_cache.dtype == out.dtype
+    assert q.dtype == k_cache.dtype == v_cache.dtype and out.dtype in (q.dtype, torch.float32)
     assert slopes is None or (slopes.dtype == torch.float32 and slopes.numel() == num_q_heads and slopes.is_cuda)
+    assert gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape[0] == n and gate.shape[1] >= num_q_heads)
+    out_f32 = 1 if out.dtype == torch.float32 and q.dtype != torch.float32 else 0
+    coef, every = query_temperature or (0.0, 0)
+    gate_stride = 0 if gate is None else (int(gate.stride(0)) if n > 1 else int(gate.shape[1]))
+    extras = (int(keep_first or 0), float(softcap or 0.0), float(coef), int(every), int(parts), int(part_strides[0]),
+              int(part_strides[1]), int(part_strides[2]), ptr(gate), gate_stride, out_f32)
     value_in_key = v_cache.data_ptr() == k_cache.data_ptr()
-    if (entries is not None and general_mma_takes(q.dtype, k_dim, v_dim) and k_dim == k_row
-            and (value_in_key or v_dim == v_row) and all(s % 8 == 0 for s in (*q_strides, *o_strides))):
+    if (entries is not None and general_mma_takes(q.dtype, k_dim, v_dim)
+            and (k_dim == k_row if parts == 1 else (not value_in_key and part_strides[1] * (parts - 1) + k_dim <= k_row))
+            and (value_in_key or v_dim == v_row)
+            and all(s % 8 == 0 for s in (*q_strides, *o_strides, *part_strides))):
         cu_tokens, starts, n_entries, max_new = entries
         run, space = general_attention_lib(k_dim, v_dim, value_in_key)
         groups = num_q_heads // nkv
-        floats = int(space(int(n_entries), int(max_new), groups, nkv, int(splits)))
+        floats = int(space(int(n_entries), int(max_new), groups, nkv * int(parts), int(splits)))
         workspace = _attention_workspace(q.device, floats) if floats else None
         check(
             run(ptr(q), int(q_strides[0]), int(q_strides[1]), ptr(k_cache), k_row, ptr(v_cache), v_row, ptr(out),
                 int(o_strides[0]), int(o_strides[1]), ptr(block_table), block_table.shape[1], page_size, num_pages, nkv,
                 int(num_q_heads), ptr(cu_tokens), ptr(starts), int(n_entries), int(max_new), ptr(slopes),
-                int(window or 0), float(scale), int(splits), ptr(workspace), ptr(status), stream()),
+                int(window or 0), float(scale), int(splits), ptr(workspace), *extras, ptr(status), stream()),
             "attention_general (tensor cores)",
         )
         if splits > 1:
@@ -513,7 +622,7 @@ def attention_general(
             ptr(q), int(q_strides[0]), int(q_strides[1]), ptr(k_cache), k_row, int(k_dim), ptr(v_cache), v_row,
             int(v_dim), ptr(out), int(o_strides[0]), int(o_strides[1]), code(q), ptr(block_table),
             block_table.shape[1], page_size, num_pages, nkv, int(num_q_heads), ptr(positions), ptr(token_entry),
-            ptr(slopes), int(window or 0), float(scale), n, ptr(status), stream(),
+            ptr(slopes), int(window or 0), float(scale), *extras, n, ptr(status), stream(),
         ),
         "attention_general",
     )
@@ -594,10 +703,11 @@ def add_rmsnorm(
     eps: float,
     row_map: torch.Tensor | None = None,
     write_residual: bool = True,
+    shift: torch.Tensor | None = None,
 ) -> None:
-    """residual += update (32-bit, in place unless ``write_residual`` is false);
-    out = rmsnorm(residual) * weight.  With ``row_map`` row r of ``out`` comes from
-    row ``row_map[r]`` of ``residual`` and ``update``."""
+    """residual += update (+ ``shift``, one 32-bit vector added to every row) (32-bit, in
+    place unless ``write_residual`` is false); out = rmsnorm(residual) * weight.  With
+    ``row_map`` row r of ``out`` comes from row ``row_map[r]`` of ``residual`` and ``update``."""
     _dense(residual, "residual"), _dense(weight, "weight"), _dense(out, "out")
     assert residual.dtype == torch.float32 and weight.dtype == torch.float32
     rows, size = out.shape
@@ -609,10 +719,11 @@ def add_rmsnorm(
         assert row_map.dtype == torch.int32 and row_map.numel() == rows
     else:
         assert residual.shape[0] == rows
+    assert shift is None or (shift.dtype == torch.float32 and shift.numel() == size and shift.is_contiguous())
     check(
         lib().fe_add_rmsnorm(
             ptr(residual), ptr(update), code(update) if update is not None else code(out),
-            ptr(weight), ptr(out), code(out), ptr(row_map), rows, size, float(eps),
+            ptr(weight), ptr(out), code(out), ptr(row_map), ptr(shift), rows, size, float(eps),
             1 if write_residual else 0, stream(),
         ),
         "add_rmsnorm",

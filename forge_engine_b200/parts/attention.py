@@ -130,10 +130,14 @@ class GQAttention(Mixer):
     @staticmethod
     def _is_general(spec) -> bool:
         """Whether the layer needs what only the general kernels do: values of another size
-        than keys, q and k normalised over the whole projection, a bias on the distance."""
+        than keys, q and k normalised over the whole projection, a bias on the distance, kept
+        first tokens, capped scores, a query temperature, a gate per head, two maps per head."""
         return (getattr(spec, "v_head_dim", None) not in (None, spec.head_dim)
                 or (spec.qk_norm and getattr(spec, "qk_norm_scope", "head") == "whole")
-                or getattr(spec, "distance_bias_base", None) is not None)
+                or getattr(spec, "distance_bias_base", None) is not None
+                or bool(getattr(spec, "keep_first", 0)) or getattr(spec, "softcap", None) is not None
+                or getattr(spec, "query_temperature", None) is not None or bool(getattr(spec, "head_gate", False))
+                or getattr(spec, "differential", None) is not None)
 
     def __init__(self, spec, weights: dict, ctx: BuildContext) -> None:
         self.general = self._is_general(spec)
@@ -150,16 +154,33 @@ class GQAttention(Mixer):
         self.nq, self.nkv, self.d = spec.num_heads, spec.num_kv_heads, spec.head_dim
         self.dv = getattr(spec, "v_head_dim", None) or self.d
         name = lambda canonical: local_name(spec, canonical)  # noqa: E731
+        # a differential layer has ``parts`` = 2 queries and keys of ``head_dim`` per head, side by side
+        self.differential = getattr(spec, "differential", None)
+        self.parts = 1 if self.differential is None else 2
+        self.head_gate = bool(getattr(spec, "head_gate", False))
+        self.keep_first = int(getattr(spec, "keep_first", 0) or 0) if spec.window else 0
+        self.softcap = getattr(spec, "softcap", None)
+        self.query_temperature = getattr(spec, "query_temperature", None)
+        if self.parts > 1 and (spec.qk_norm or spec.bias or getattr(spec.position, "kind", "none") != "none"):
+            raise ConfigError("a differential layer takes no q/k norm, no bias and no rotation")
         bias = None
-        rows = [self.nq * self.d, self.nkv * self.d, self.nkv * self.dv]
+        rows = [self.nq * self.parts * self.d, self.nkv * self.parts * self.d, self.nkv * self.dv]
+        names = [name("q_proj.weight"), name("k_proj.weight"), name("v_proj.weight")]
+        if self.head_gate:
+            # the gates' logits are further columns of the same product
+            rows.append(self.nq)
+            names.append(name("gate_proj.weight"))
         if spec.bias:
+            if self.head_gate:
+                raise ConfigError("a gate per head together with biases is not implemented")
             bias = fused_rows(weights, [name("q_proj.bias"), name("k_proj.bias"), name("v_proj.bias")], rows)
         # q, k and v are looked up one at a time and copied into the fused tensor
-        self.qkv_proj = Linear(
-            fused_rows(weights, [name("q_proj.weight"), name("k_proj.weight"), name("v_proj.weight")], rows),
-            bias,
-            status=ctx.status,
-        )
+        self.qkv_proj = Linear(fused_rows(weights, names, rows), bias, status=ctx.status)
+        self.diff_lambda = None
+        if self.differential is not None:
+            vectors = [weights[name(n)].float() for n in ("lambda_q1", "lambda_k1", "lambda_q2", "lambda_k2")]
+            first, second = (vectors[0] * vectors[1]).sum(), (vectors[2] * vectors[3]).sum()
+            self.diff_lambda = float((torch.exp(first) - torch.exp(second)).item() + float(self.differential.offset))
         self.o_proj = Linear(weights[name("o_proj.weight")], weights[name("o_proj.bias")] if spec.bias else None,
                              status=ctx.status)
         self.q_norm = self.k_norm = None
@@ -173,13 +194,15 @@ class GQAttention(Mixer):
             heads = torch.arange(1, self.nq + 1, dtype=torch.float64)
             self.slopes = (float(base) ** (-heads / self.nq)).float().to(ctx.device).contiguous()
         self._slots = None
-        self.plan_key = ("gqa_attention", self.nq, self.nkv, self.d, spec.window) + (("general", self.dv) if self.general else ())
+        self.plan_key = ("gqa_attention", self.nq, self.nkv, self.d, spec.window) + (
+            ("general", self.dv, self.parts, self.keep_first) if self.general else ())
         self.last_splits = None   # what the last step's decode entries ran with (0: balanced kernel)
 
     @classmethod
     def weight_shapes(cls, spec) -> dict:
         dv = getattr(spec, "v_head_dim", None) or spec.head_dim
-        q, kv, h = spec.num_heads * spec.head_dim, spec.num_kv_heads * spec.head_dim, spec.hidden_size
+        parts = 1 if getattr(spec, "differential", None) is None else 2
+        q, kv, h = spec.num_heads * parts * spec.head_dim, spec.num_kv_heads * parts * spec.head_dim, spec.hidden_size
         name = lambda canonical: local_name(spec, canonical)  # noqa: E731
         shapes = {
             name("q_proj.weight"): WeightInfo((q, h)),
@@ -187,6 +210,11 @@ class GQAttention(Mixer):
             name("v_proj.weight"): WeightInfo((spec.num_kv_heads * dv, h)),
             name("o_proj.weight"): WeightInfo((h, spec.num_heads * dv)),
         }
+        if getattr(spec, "head_gate", False):
+            shapes[name("gate_proj.weight")] = WeightInfo((spec.num_heads, h))
+        if parts > 1:
+            for vector in ("lambda_q1", "lambda_k1", "lambda_q2", "lambda_k2"):
+                shapes[name(vector)] = WeightInfo((spec.head_dim,), "bias")
         if spec.qk_norm:
             whole = getattr(spec, "qk_norm_scope", "head") == "whole"
             shapes[name("q_norm.weight")] = WeightInfo((q if whole else spec.head_dim,), "norm")
@@ -199,8 +227,9 @@ class GQAttention(Mixer):
         return shapes
 
     def cache_needs(self) -> CacheNeeds:
-        return CacheNeeds(kv=PagedKVSpec(self.nkv, self.d, self.spec.window,
-                                         None if self.dv == self.d else self.dv))
+        key = self.parts * self.d          # a differential layer caches both keys of a head in one row
+        return CacheNeeds(kv=PagedKVSpec(self.nkv, key, self.spec.window, None if self.dv == key else self.dv,
+                                         self.keep_first))
 
     def decode_slots(self) -> int:
         """Blocks of the decode kernels this device holds at once: what the balanced kernel
@@ -252,7 +281,8 @@ class GQAttention(Mixer):
         position encoding is a rotation, and stores k and v in their pages; the attention
         kernel takes the distance bias and any key and value size."""
         n = x.shape[0]
-        nq, nkv, d, dv = self.nq, self.nkv, self.d, self.dv
+        nq, nkv, dv = self.nq, self.nkv, self.dv
+        d = self.d * self.parts              # what a head's query and key rows hold
         k_cache, v_cache = cache.kv
         table = batch.group_tables[cache.group]
         with self.ctx.section("mixer.qkv_rope_cache"):
@@ -271,20 +301,30 @@ class GQAttention(Mixer):
             native.qkv_prepare(
                 q=qkv[:, :q_end], q_heads=nq, q_dim=d, q_norm=(mode, d, self.q_norm), q_out=q, q_out_strides=(nq * d, d),
                 k=qkv[:, q_end:k_end] if cache.owns else None, k_heads=nkv, k_dim=d, k_norm=(mode, d, self.k_norm),
-                v=qkv[:, k_end:] if cache.owns else None, v_dim=dv, eps=self.spec.qk_norm_eps,
+                v=qkv[:, k_end : k_end + nkv * dv] if cache.owns else None, v_dim=dv, eps=self.spec.qk_norm_eps,
                 table=angles, rot_dims=rot_dims, interleaved=getattr(self.position, "interleaved", False),
                 k_cache=k_cache, v_cache=v_cache, block_table=table, positions=batch.positions,
                 token_entry=batch.token_entry, status=self.ctx.status,
             )
-        out = torch.empty((n, nq * dv), dtype=k_cache.dtype, device=x.device)
+        parts = self.parts
+        # a differential layer's maps are kept in 32-bit side by side until they are combined
+        out = torch.empty((n, nq * parts * dv), dtype=k_cache.dtype if parts == 1 else torch.float32, device=x.device)
         if self.plan_key not in batch.plans:
             self.plan_step(batch.entries, k_cache.shape[2], batch.plans)
         with self.ctx.section("mixer.attention"):
-            native.attention_general(q, (nq * d, d), k_cache, d, v_cache, dv, out, (nq * dv, dv), table,
+            native.attention_general(q, (nq * d, d), k_cache, self.d, v_cache, dv, out, (nq * parts * dv, parts * dv), table,
                                      batch.positions, batch.token_entry, nq, self.slopes, self.spec.window,
                                      self.spec.scale, self.ctx.status,
                                      entries=(batch.cu_tokens, batch.starts, batch.n_entries, batch.max_new),
-                                     splits=batch.plans[self.plan_key])
+                                     splits=batch.plans[self.plan_key], keep_first=self.keep_first,
+                                     softcap=self.softcap, query_temperature=self.query_temperature, parts=parts,
+                                     part_strides=(self.d, self.d, dv) if parts > 1 else (0, 0, 0),
+                                     gate=qkv[:, k_end + nkv * dv :] if self.head_gate else None)
+            if parts > 1:
+                maps = out
+                out = torch.empty((n, nq * dv), dtype=k_cache.dtype, device=x.device)
+                native.differential_combine(maps, out, dv, self.diff_lambda, self.differential.eps,
+                                            1.0 - float(self.differential.offset))
         return out
 
     def _project(self, x, batch, cache: CacheView):
@@ -368,7 +408,8 @@ class GQAttention(Mixer):
             if self.plan_key not in plans:
                 splits = 1
                 if native.general_mma_takes(self.ctx.dtype, self.d, self.dv):
-                    splits = native.general_splits(entries, self.nq // self.nkv, self.nkv, self.spec.window)
+                    splits = native.general_splits(entries, self.nq // self.nkv, self.nkv * self.parts, self.spec.window,
+                                                   keep_first=self.keep_first)
                 plans[self.plan_key] = splits
             return
         if self.ctx.dtype != torch.bfloat16 or self.plan_key in plans:

@@ -27,14 +27,18 @@ class PreNormBlock:
         self.ctx = ctx
         self.input_norm = build_part(spec.input_norm, weights["input_norm"], ctx)
         self.mixer = build_part(spec.mixer, weights["mixer"], ctx)
-        self.post_norm = build_part(spec.post_norm, weights["post_norm"], ctx)
-        self.ffn = build_part(spec.ffn, weights["ffn"], ctx)
+        # a layer without a feed-forward is the first half alone: h += mixer(norm1(h))
+        self.post_norm = self.ffn = None
+        if spec.ffn is not None:
+            self.post_norm = build_part(spec.post_norm, weights["post_norm"], ctx)
+            self.ffn = build_part(spec.ffn, weights["ffn"], ctx)
         self._chain_parts = None
 
     @classmethod
     def weight_shapes(cls, spec) -> dict:
         """role -> {local name -> WeightInfo}"""
-        return {role: part_class(getattr(spec, role)).weight_shapes(getattr(spec, role)) for role in cls.roles}
+        return {role: part_class(getattr(spec, role)).weight_shapes(getattr(spec, role)) for role in cls.roles
+                if getattr(spec, role) is not None}
 
     def cache_needs(self):
         return self.mixer.cache_needs()
@@ -47,7 +51,7 @@ class PreNormBlock:
     @property
     def graph_safe(self) -> bool:
         return all(getattr(part, "graph_safe", False)
-                   for part in (self.input_norm, self.mixer, self.post_norm, self.ffn))
+                   for part in (self.input_norm, self.mixer, self.post_norm, self.ffn) if part is not None)
 
     def _chain(self):
         """What the one-kernel form of "output projection, norm, feed-forward" needs of this
@@ -73,10 +77,23 @@ class PreNormBlock:
                     self._chain_parts = (o_proj, norm, gate_up, down)
         return self._chain_parts or None
 
-    def forward(self, h, pending, batch, cache: CacheView):
+    def forward(self, h, pending, batch, cache: CacheView, shift=None):
         """``h`` 32-bit [N, hidden] (in place); ``pending`` the previous block's update or
-        None.  Returns this block's feed-forward update, still to be added (None when it
-        has already been added)."""
+        None; ``shift`` None or a 32-bit vector that is added to every row of ``h`` before
+        anything else (in the first norm's kernel).  Returns this block's last update, still
+        to be added (None when it has already been added)."""
+        if shift is not None or self.ffn is None:
+            with self.ctx.section("input_norm"):
+                normed = self.input_norm.add_forward(h, pending, shift=shift) if shift is not None \
+                    else self.input_norm.add_forward(h, pending)
+            with self.ctx.section("mixer"):
+                update = self.mixer.forward(normed, batch, cache)
+            if self.ffn is None:
+                return update
+            with self.ctx.section("post_norm"):
+                normed = self.post_norm.add_forward(h, update)
+            with self.ctx.section("ffn"):
+                return self.ffn.forward(normed)
         chain = self._chain() if batch.n_tokens <= native.CHAIN_MAX_TOKENS and self.ctx.timer is None else None
         if chain is not None:
             # few tokens: output projection (+= h), norm + gate/up with SiLU*mul and the down

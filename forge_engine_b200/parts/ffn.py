@@ -1,5 +1,6 @@
 """Gated feed-forward: down(act(gate(x)) * up(x)) with act = SiLU
-(src/forge_engine/qwen3.py:210-227) or the tanh form of GELU.
+(src/forge_engine/qwen3.py:210-227) or the tanh form of GELU, or the clamped unit
+down(g' sigmoid(slope g') (u' + 1)) with g' = min(gate(x), limit), u' = clamp(up(x), +-limit).
 gate and up are one fused projection; the activation product is one kernel."""
 
 from __future__ import annotations
@@ -13,7 +14,7 @@ from .base import BuildContext, FeedForward, WeightInfo, register_part
 from .linear import Linear, fused_rows, interleaved_rows
 
 GATE_UP_BLOCK = 16
-ACTIVATIONS = {"silu": native.ACT_SILU, "gelu_tanh": native.ACT_GELU_TANH}
+ACTIVATIONS = {"silu": native.ACT_SILU, "gelu_tanh": native.ACT_GELU_TANH, "clamped_swish": native.ACT_CLAMPED_SWISH}
 
 
 class GatedMLP(FeedForward):
@@ -23,6 +24,10 @@ class GatedMLP(FeedForward):
         if spec.activation not in ACTIVATIONS:
             raise ConfigError(f"activation {spec.activation!r} is not implemented; known: {', '.join(ACTIVATIONS)}")
         self.activation = ACTIVATIONS[spec.activation]
+        self.limit = float(getattr(spec, "limit", None) or 0.0)
+        self.slope = float(getattr(spec, "slope", 1.0))
+        if self.activation == native.ACT_CLAMPED_SWISH and self.limit <= 0.0:
+            raise ConfigError("the clamped unit needs a positive limit")
         self.inter = spec.intermediate_size
         gate, up, down = (local_name(spec, n) for n in ("gate_proj.weight", "up_proj.weight", "down_proj.weight"))
         # Rows of the fused weight alternate 16 gate and 16 up features where the size allows:
@@ -54,14 +59,16 @@ class GatedMLP(FeedForward):
         return self.down.add_into(self.gate_up.silu_mul(x, self.block), residual)
 
     def forward(self, x):
-        act = self.gate_up.silu_mul(x, self.block, self.activation) if self.block else None
+        fused = self.block and self.activation in (native.ACT_SILU, native.ACT_GELU_TANH)
+        act = self.gate_up.silu_mul(x, self.block, self.activation) if fused else None
         if act is None:
             act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
             if self.activation == native.ACT_SILU:
                 native.silu_mul(self.gate_up(x), act, self.block)
             else:
                 # the activation is taken of the 32-bit sums of the projection, not of their rounding
-                native.act_mul(self.gate_up(x, out_dtype=torch.float32), act, self.activation, self.block)
+                native.act_mul(self.gate_up(x, out_dtype=torch.float32), act, self.activation, self.block,
+                               self.limit, self.slope)
         return self.down(act)
 
 

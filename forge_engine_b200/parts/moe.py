@@ -1,0 +1,119 @@
+"""A routed feed-forward: per token the ``top`` of ``experts`` gated units with the largest
+router scores, and optionally a shared unit that every token uses.
+
+The router's logits are a true 32-bit product.  Everything after them stays on the device:
+the (token, choice) pairs are laid out by expert, two grouped products run over them (gate
+and up with the gated unit in the epilogue; down), and one kernel sums a token's rows and
+adds the shared unit's output times its sigmoid gate.  Nothing is decided on the host, so a
+step replays from a CUDA graph.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..config.specs import local_name
+from ..errors import ConfigError
+from ..ops import native
+from .base import BuildContext, FeedForward, WeightInfo, build_part, part_class, register_part
+from .ffn import ACTIVATIONS
+
+MAX_TOP = 32
+
+
+def _shared_spec(spec):
+    """The shared unit's spec with its tensors under ``shared.``."""
+    import dataclasses
+
+    renamed = tuple((canonical, "shared." + local_name(spec.shared, canonical))
+                    for canonical in ("gate_proj.weight", "up_proj.weight", "down_proj.weight"))
+    return dataclasses.replace(spec.shared, rename=renamed)
+
+
+class RoutedMLP(FeedForward):
+    graph_safe = True
+
+    def __init__(self, spec, weights: dict, ctx: BuildContext) -> None:
+        if spec.score not in ("sigmoid", "softmax"):
+            raise ConfigError(f"router score {spec.score!r}; known: sigmoid, softmax")
+        if spec.weight_on not in ("input", "output"):
+            raise ConfigError(f"weight_on={spec.weight_on!r}; known: input, output")
+        if not 1 <= spec.top <= min(spec.experts, MAX_TOP):
+            raise ConfigError(f"top={spec.top} of {spec.experts} experts; at most {MAX_TOP}")
+        unit = spec.expert
+        if unit.activation not in ACTIVATIONS:
+            raise ConfigError(f"activation {unit.activation!r} is not implemented")
+        self.ctx = ctx
+        self.experts, self.top, self.width, self.inter = spec.experts, spec.top, spec.hidden_size, unit.intermediate_size
+        self.softmax, self.renormalise = spec.score == "softmax", bool(spec.renormalise)
+        self.weight_on_input = spec.weight_on == "input"
+        self.activation = ACTIVATIONS[unit.activation]
+        self.limit, self.slope = float(unit.limit or 0.0), float(unit.slope)
+        # the router's rows, and under them the shared unit's gate row: one 32-bit product
+        rows = [weights["router"]]
+        self.shared = None
+        self.shared_gate = False
+        if spec.shared is not None:
+            self.shared_gate = bool(spec.shared_gate)
+            if self.shared_gate:
+                rows.append(weights["shared.sg"].reshape(1, -1))
+        self.router = torch.cat([r.float() for r in rows], dim=0).contiguous()
+        del rows
+        names = [local_name(unit, n) for n in ("gate_proj.weight", "up_proj.weight", "down_proj.weight")]
+        stacks = []
+        for name, shape in zip(names, ((self.inter, self.width), (self.inter, self.width), (self.width, self.inter))):
+            stack = None
+            for e in range(self.experts):
+                tensor = weights[f"e{e}.{name}"]
+                if stack is None:
+                    stack = torch.empty((self.experts, *shape), dtype=tensor.dtype, device=tensor.device)
+                stack[e].copy_(tensor)
+                del tensor
+            stacks.append(stack)
+        self.gate, self.up, self.down = stacks
+        if spec.shared is not None:
+            self.shared = build_part(_shared_spec(spec), weights, ctx)
+        self.counts = torch.zeros(self.experts, dtype=torch.int32, device=ctx.device)
+
+    @classmethod
+    def weight_shapes(cls, spec) -> dict:
+        h, unit = spec.hidden_size, spec.expert
+        shapes = {"router": WeightInfo((spec.experts, h))}
+        names = [local_name(unit, n) for n in ("gate_proj.weight", "up_proj.weight", "down_proj.weight")]
+        for e in range(spec.experts):
+            shapes[f"e{e}.{names[0]}"] = WeightInfo((unit.intermediate_size, h))
+            shapes[f"e{e}.{names[1]}"] = WeightInfo((unit.intermediate_size, h))
+            shapes[f"e{e}.{names[2]}"] = WeightInfo((h, unit.intermediate_size))
+        if spec.shared is not None:
+            shared = _shared_spec(spec)
+            shapes.update(part_class(shared).weight_shapes(shared))
+            if spec.shared_gate:
+                shapes["shared.sg"] = WeightInfo((1, h))
+        return shapes
+
+    def forward(self, x):
+        n = x.shape[0]
+        slots = n * self.top
+        device = x.device
+        logits = torch.empty((n, self.router.shape[0]), dtype=torch.float32, device=device)
+        native.gemm_simt(x, self.router, logits)
+        max_tiles = native.moe_max_tiles(slots, self.experts)
+        ints = torch.empty(4 * slots + self.experts + 1 + 2 * max_tiles, dtype=torch.int32, device=device)
+        weight = torch.empty(slots, dtype=torch.float32, device=device)
+        self.counts.zero_()
+        plan = native.moe_route(logits, self.experts, self.top, self.softmax, self.renormalise, self.counts, ints,
+                                weight, max_tiles)
+        hidden = torch.empty((slots, self.inter), dtype=x.dtype, device=device)
+        native.moe_grouped(x, self.gate, self.up, hidden, plan, self.top, max_tiles, gather=True,
+                           slot_weight=weight if self.weight_on_input else None, act=self.activation,
+                           limit=self.limit, slope=self.slope)
+        rows = torch.empty((slots, self.width), dtype=torch.float32, device=device)
+        native.moe_grouped(hidden, self.down, None, rows, plan, self.top, max_tiles, gather=False)
+        shared = None if self.shared is None else self.shared.forward(x)
+        out = torch.empty((n, self.width), dtype=torch.float32, device=device)
+        native.moe_combine(rows, plan, self.top, out, slot_weight=None if self.weight_on_input else weight,
+                           shared=shared, shared_logit=logits[:, self.experts] if self.shared_gate else None)
+        return out
+
+
+register_part("routed_mlp", RoutedMLP, replace=True)

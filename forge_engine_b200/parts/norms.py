@@ -25,14 +25,14 @@ class RMSNorm(Norm):
     def weight_shapes(cls, spec) -> dict:
         return {local_name(spec, "weight"): WeightInfo((spec.size,), "norm")}
 
-    def add_forward(self, residual, update, row_map=None):
-        """residual (32-bit [N, size]) += update; returns the normalised rows in the
-        activation dtype.  With ``row_map`` only those rows are produced and the
-        residual is left untouched."""
+    def add_forward(self, residual, update, row_map=None, shift=None):
+        """residual (32-bit [N, size]) += update (+ ``shift``, a 32-bit vector added to every
+        row); returns the normalised rows in the activation dtype.  With ``row_map`` only
+        those rows are produced and the residual is left untouched."""
         rows = residual.shape[0] if row_map is None else row_map.numel()
         out = torch.empty((rows, self.size), dtype=self.dtype, device=residual.device)
         native.add_rmsnorm(residual, update, self.weight, out, self.eps, row_map,
-                           write_residual=row_map is None)
+                           write_residual=row_map is None, shift=shift)
         return out
 
     def forward(self, x):
