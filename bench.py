@@ -535,8 +535,9 @@ DESIGN_SIZES = {
 
 def design_compare(args) -> int:
     """Prefill (one 2,048-token prompt) and decode (batch 8, 2,048-token contexts) of models
-    of `--layers` (4) layers of one kind: the Qwen3 layer, and the Zofadra attention, latent
-    attention and linear-recurrence layers at the same sizes, plus a model that mixes them.
+    of `--layers` (4) layers of one kind: the Qwen3 layer, the Zofadra attention, latent
+    attention and linear-recurrence layers and the Tekilorn differential, gated window and
+    routed layers at the same sizes, plus a model of each design that mixes its layers.
     One JSON line per model: tokens/s, ms per step, the median device time of every part of a
     step (CUDA events round each part, in a second runner) and, for the token-mixing kernel,
     its share of the measured peaks (prefill: its flops over the library GEMM's burst rate;
@@ -581,6 +582,36 @@ def design_compare(args) -> int:
             "zofadra-recurrence": zofadra([recurrence] * layers),
             "zofadra-mixed": zofadra([latent, attention, recurrence, shared, attention][:max(layers, 5)]),
         }
+        # Tekilorn at the same projection sizes: the differential layer has half the heads, each
+        # with two queries and keys of D and values of 2 D; the routed feed-forward has as many
+        # active weights per token as the dense one (2 of 16 experts of ff / 4, a shared unit of ff / 2)
+        keep = 4
+        unit = {"kind": "dense", "ff": z["ff"], "limit": 7.0}
+        routed = {"kind": "moe", "router": {"experts": 16, "top": 2}, "expert": {"ff": z["ff"] // 4, "limit": 7.0},
+                  "shared": {"ff": z["ff"] // 2, "limit": 7.0}}
+        differential = {"type": "attention", "mlp": unit, "mixer": {
+            "heads": H // 2, "kv_heads": G // 2, "dim": D, "vdim": 2 * D, "diff": 0.3, "scale": D ** -0.5, "softcap": 30.0,
+            "q_temp": {"coef": 0.5, "every": 128}}}
+        gated = {"type": "attention_2", "mlp": unit, "mixer": {
+            "heads": H, "kv_heads": G, "dim": D, "vdim": D, "scale": D ** -0.5, "rot": {"base": 1e6, "dims": D},
+            "mask": {"size": window, "keep_first": keep}}}
+
+        def tekilorn(kinds, loop=None):
+            raw = {"architecture": "Tekilorn", "vocab": vocab, "width": W, "norm": {"eps": 1e-5}, "layers": kinds}
+            if loop:
+                raw["loop"] = loop
+            return raw
+
+        models.update({
+            "tekilorn-differential": tekilorn([differential] * layers),
+            "tekilorn-window": tekilorn([gated] * layers),
+            "tekilorn-routed": tekilorn([dict(gated, mlp=routed)] * layers),
+            "tekilorn-mixed": tekilorn([differential, dict(gated, mlp=routed), dict(gated, mlp=routed), gated],
+                                       loop={"start": 1, "stop": 3, "times": 2}),
+        })
+        if args.design_models:
+            wanted = [w for w in args.design_models.split(",") if w]
+            models = {name: raw for name, raw in models.items() if any(name.startswith(w) for w in wanted)}
         rank, rot = lat["kv_rank"], lat["rot_dim"]
         seen = lambda span: sum(min(i + 1, span) for i in range(CONTEXT))          # noqa: E731  keys all queries see
         mixer_cost = {     # (flops of a 2,048-token prompt, bytes a decode step must move) per layer
@@ -589,9 +620,16 @@ def design_compare(args) -> int:
             "zofadra-attention": (4 * H * D * seen(window), batch * window * G * 2 * D * 2),
             "zofadra-latent": (2 * H * (2 * rank + rot) * seen(CONTEXT), batch * CONTEXT * (rank + rot) * 2),
             "zofadra-recurrence": (4 * H * rec["dim"] * rec["vdim"] * CONTEXT, batch * H * rec["dim"] * rec["vdim"] * 4 * 2),
+            # H maps of D over values of 2 D; per token G / 2 key rows of 2 D and G / 2 value rows of 2 D
+            "tekilorn-differential": (H * (2 * D + 4 * D) * seen(CONTEXT), batch * CONTEXT * (G // 2) * 4 * D * 2),
+            "tekilorn-window": (4 * H * D * sum(min(i + 1, window) + max(0, min(keep, i + 1 - window)) for i in range(CONTEXT)),
+                                batch * (window + keep) * G * 2 * D * 2),
         }
+        mixer_cost["tekilorn-routed"] = mixer_cost["tekilorn-window"]
         mixer_part = {"qwen3": "mixer.attention", "qwen3-window": "mixer.attention", "zofadra-attention": "mixer.attention",
-                      "zofadra-latent": "mixer.attention", "zofadra-recurrence": "mixer.recurrence"}
+                      "zofadra-latent": "mixer.attention", "zofadra-recurrence": "mixer.recurrence",
+                      "tekilorn-differential": "mixer.attention", "tekilorn-window": "mixer.attention",
+                      "tekilorn-routed": "mixer.attention"}
         for name, raw in models.items():
             n_layers = len(raw["layers"]) if "layers" in raw else raw["num_hidden_layers"]
             pages = batch * (-(-(CONTEXT + 64) // PAGE) + 1) + -(-CONTEXT // PAGE) + 8
@@ -704,7 +742,10 @@ def main() -> int:
                         help="only the mixed step: 8 requests decoding beside a prompt portion, TOKENS tokens in all "
                              "(with --kernel-times: the kernels of one such step)")
     parser.add_argument("--design-compare", metavar="WIDTH", choices=sorted(DESIGN_SIZES) + ["all"],
-                        help="prefill and decode of the Zofadra layer kinds beside the Qwen3 layer at equal size")
+                        help="prefill and decode of the Zofadra and Tekilorn layer kinds beside the Qwen3 layer at equal size")
+    parser.add_argument("--design-models", metavar="NAMES", default="",
+                        help="with --design-compare: only the models whose names start with one of these (comma-separated), "
+                             "e.g. qwen3,tekilorn")
     parser.add_argument("--kernel-times", action="store_true",
                         help="also print the device time of every kernel of one more step (for profiles/)")
     args = parser.parse_args()

@@ -241,3 +241,53 @@ def random_weights(config: dict, seed: int, dtype=torch.bfloat16) -> dict:
             t = gain * torch.randn(shape, generator=gen) / math.sqrt(shape[-1])
         out[name] = t.to(dtype)
     return out
+
+
+# ---------------------------------------------------------------------------
+# builders of small configurations
+# ---------------------------------------------------------------------------
+def dense(ff=48, limit=1.25):
+    return {"kind": "dense", "ff": ff, "limit": limit}
+
+
+def routed(experts=5, top=2, ff=24, limit=1.25, shared_ff=40, shared_limit=2.0):
+    mlp = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff, "limit": limit}}
+    if shared_ff is not None:
+        mlp["shared"] = {"ff": shared_ff, "limit": shared_limit}
+    return mlp
+
+
+def differential_layer(heads=4, kv_heads=2, dim=16, vdim=32, diff=0.25, softcap=20.0, q_temp=(0.4, 8), scale=None,
+                       mlp="dense"):
+    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "diff": diff,
+             "scale": scale if scale is not None else dim ** -0.5}
+    if softcap is not None:
+        mixer["softcap"] = softcap
+    if q_temp is not None:
+        mixer["q_temp"] = {"coef": q_temp[0], "every": q_temp[1]}
+    return {"type": "attention", "mixer": mixer, "mlp": dense() if mlp == "dense" else mlp}
+
+
+def window_layer(heads=4, kv_heads=2, dim=16, vdim=16, window=9, keep_first=3, rot_dims=8, base=100.0, scale=None,
+                 mlp="dense"):
+    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim,
+             "scale": scale if scale is not None else dim ** -0.5}
+    if rot_dims:
+        mixer["rot"] = {"dims": rot_dims, "base": base}
+    if window is not None:
+        mixer["mask"] = {"size": window, "keep_first": keep_first}
+    return {"type": "attention_2", "mixer": mixer, "mlp": dense() if mlp == "dense" else mlp}
+
+
+def config(layers, width=64, vocab=97, eps=1e-5, loop=None) -> dict:
+    cfg = {"architecture": "Tekilorn", "vocab": vocab, "width": width, "norm": {"eps": eps}, "layers": list(layers)}
+    if loop is not None:
+        cfg["loop"] = {"start": loop[0], "stop": loop[1], "times": loop[2]}
+    return cfg
+
+
+def greedy_generate(cfg: dict, weights: dict, prompt, count: int) -> list:
+    ids = list(prompt)
+    for _ in range(count):
+        ids.append(int(forward(cfg, weights, ids)[-1].argmax()))
+    return ids[len(prompt):]
