@@ -37,7 +37,13 @@ constexpr int THREADS = 192;
 // block (tokens x 128 features) must fit in its ring of stages (128 tokens: 64 of 96 KB).
 constexpr int CLUSTER_REDUCE_TOKENS = 128;
 
-enum Epilogue { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_ADD_F32 = 2, EPI_SILU_MUL_BF16 = 3, EPI_QKV_ROPE = 4, EPI_GELU_MUL_BF16 = 5 };
+enum Epilogue { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_ADD_F32 = 2, EPI_SILU_MUL_BF16 = 3, EPI_QKV_ROPE = 4, EPI_GELU_MUL_BF16 = 5,
+                EPI_CLAMP_MUL_BF16 = 6 };
+
+// the epilogues that turn rows of alternating gate and up features into one gated value
+__host__ __device__ constexpr bool is_gated(int epi) {
+  return epi == EPI_SILU_MUL_BF16 || epi == EPI_GELU_MUL_BF16 || epi == EPI_CLAMP_MUL_BF16;
+}
 
 // What the fused q/k/v projection needs beyond the product (EPI_QKV_ROPE; head size 128, so
 // that a 128-feature tile is one head): per-head RMS norm of q and k with one [128] weight
@@ -71,6 +77,14 @@ struct GemmParams {
   unsigned wait_limit;   // polls a wait may take before the block gives up
   int skip_kblock;       // test fault: the producer leaves out the load of this k-block (-1: none)
   QkvRope rope;          // EPI_QKV_ROPE only
+  float act_limit, act_slope;   // EPI_CLAMP_MUL_BF16: g' sigmoid(slope g') (u' + 1), g' = min(g, limit), u' = clamp(u, +-limit)
+  // Grouped form (null: the plain product): the token rows are sorted by expert, w stacks the
+  // experts' [o, k] matrices, and the block of row tile blockIdx.y works for expert
+  // g_expert[blockIdx.y] (negative: no such tile, the block returns) on the rows from
+  // g_row[blockIdx.y] up to the expert's last one, g_offsets[expert + 1] - 1, at most BN of them.
+  const int* g_expert;
+  const int* g_row;
+  const int* g_offsets;
 };
 
 template <int BN, int EPI = 0> __host__ __device__ constexpr int stages_for() {
@@ -98,10 +112,20 @@ template <int EPI> __device__ __forceinline__ float gate_act(float x) {
   return silu_f(x);
 }
 
+// The gated value of one feature from its gate and up sums.
+template <int EPI> __device__ __forceinline__ float gated(float g, float u, const GemmParams& p) {
+  if (EPI == EPI_CLAMP_MUL_BF16) {
+    g = fminf(g, p.act_limit);
+    u = fminf(fmaxf(u, -p.act_limit), p.act_limit);
+    return g / (1.f + expf(-p.act_slope * g)) * (u + 1.f);
+  }
+  return gate_act<EPI>(g) * u;
+}
+
 // Finished values of one accumulator row (feature) for 16 consecutive tokens.
 template <int EPI>
 __device__ __forceinline__ void store16(const GemmParams& p, float (&v)[16], int feature, int token0, int lane) {
-  if (EPI == EPI_SILU_MUL_BF16 || EPI == EPI_GELU_MUL_BF16) {
+  if (is_gated(EPI)) {
     // weight rows alternate 16 gate features, 16 up features: lanes 0-15 hold gate,
     // lanes 16-31 the matching up.  The lower half-warp finishes even tokens, the upper
     // half odd ones, so both halves store.
@@ -113,7 +137,7 @@ __device__ __forceinline__ void store16(const GemmParams& p, float (&v)[16], int
       const float send = lane < 16 ? v[j + 1] : v[j];
       const float recv = __shfl_xor_sync(0xffffffffu, send, 16);
       const int token = token0 + j + (lane < 16 ? 0 : 1);
-      const float r = lane < 16 ? gate_act<EPI>(v[j]) * recv : gate_act<EPI>(recv) * v[j + 1];
+      const float r = lane < 16 ? gated<EPI>(v[j], recv, p) : gated<EPI>(recv, v[j + 1], p);
       if (token < p.n && out_feature < half_o) y[(size_t)token * half_o + out_feature] = __float2bfloat16_rn(r);
     }
     return;
@@ -189,13 +213,13 @@ __device__ __forceinline__ void rope_token(const GemmParams& p, float v, int hea
 // lanes of the warp call it for the same token.
 template <int EPI>
 __device__ __forceinline__ void store_one(const GemmParams& p, float v, int feature, int token, int lane) {
-  if (EPI == EPI_SILU_MUL_BF16 || EPI == EPI_GELU_MUL_BF16) {
+  if (is_gated(EPI)) {
     // lanes 0-15 hold 16 gate features, lanes 16-31 the matching up features
     const float up = __shfl_xor_sync(0xffffffffu, v, 16);
     const int half_o = p.o >> 1;
     const int out_feature = (feature >> 5) * 16 + (lane & 15);
     if (lane < 16 && token < p.n && out_feature < half_o)
-      reinterpret_cast<bf16*>(p.y)[(size_t)token * half_o + out_feature] = __float2bfloat16_rn(gate_act<EPI>(v) * up);
+      reinterpret_cast<bf16*>(p.y)[(size_t)token * half_o + out_feature] = __float2bfloat16_rn(gated<EPI>(v, up, p));
     return;
   }
   if (feature >= p.o || token >= p.n) return;
@@ -228,7 +252,17 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
   float* exchange = reinterpret_cast<float*>(last_flag + 2);     // EPI_QKV_ROPE: 2 x 136 floats
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+  const int m0 = blockIdx.x * BM;
+  int n0 = blockIdx.y * BN, w0 = m0;       // first token row; first row of the weight tile in w
+  if (p.g_expert != nullptr) {
+    // the table of row tiles comes from the kernel before this one
+    pdl_wait();
+    const int expert = p.g_expert[blockIdx.y];
+    if (expert < 0) return;                // all threads alike, before anything is set up
+    n0 = p.g_row[blockIdx.y];
+    p.n = min(p.g_offsets[expert + 1], n0 + BN);     // rows beyond belong to the next expert
+    w0 = expert * p.o + m0;
+  }
   const int kblocks = (p.k + BK - 1) / BK;
   const int per_split = (kblocks + p.ksplit - 1) / p.ksplit;
   const int kb_begin = blockIdx.z * per_split;
@@ -264,7 +298,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
       for (int i = 0; i < ahead; ++i) {
         if (kb_begin + i == p.skip_kblock) continue;      // test fault: this stage never fills
         mbar_expect_tx(full + i, A_BYTES + B_BYTES);
-        tma_load_2d(a_tiles + i * A_BYTES, &map_w, (kb_begin + i) * BK, m0, full + i);
+        tma_load_2d(a_tiles + i * A_BYTES, &map_w, (kb_begin + i) * BK, w0, full + i);
       }
       pdl_wait();
       for (int i = 0; i < ahead; ++i)
@@ -276,7 +310,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         if (kb_begin + i == p.skip_kblock) continue;      // test fault: this stage never fills
         mbar_expect_tx(full + s, A_BYTES + B_BYTES);
         const int kcoord = (kb_begin + i) * BK;
-        tma_load_2d(a_tiles + s * A_BYTES, &map_w, kcoord, m0, full + s);
+        tma_load_2d(a_tiles + s * A_BYTES, &map_w, kcoord, w0, full + s);
         tma_load_2d(b_tiles + s * B_BYTES, &map_x, kcoord, n0, full + s);
       }
     }
@@ -552,6 +586,7 @@ int launch_bn(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p,
     case EPI_ADD_F32: return launch_one<BN, EPI_ADD_F32>(mw, mx, p, grid, stream);
     case EPI_SILU_MUL_BF16: return launch_one<BN, EPI_SILU_MUL_BF16>(mw, mx, p, grid, stream);
     case EPI_GELU_MUL_BF16: return launch_one<BN, EPI_GELU_MUL_BF16>(mw, mx, p, grid, stream);
+    case EPI_CLAMP_MUL_BF16: return launch_one<BN, EPI_CLAMP_MUL_BF16>(mw, mx, p, grid, stream);
     case EPI_QKV_ROPE:
       if (BN <= 64) return launch_one<(BN <= 64 ? BN : 16), EPI_QKV_ROPE>(mw, mx, p, grid, stream);
       return FE_ERR_BAD_SHAPE;
@@ -577,19 +612,30 @@ FE_EXPORT void fe_gemm_tc5_set_test_fault(unsigned wait_limit, int skip_kblock) 
 // Token-tile width the kernel uses for n tokens.
 FE_EXPORT int fe_gemm_tc5_tile(int n) { return n <= 16 ? 16 : (n <= 32 ? 32 : (n <= 64 ? 64 : (n <= 128 ? 128 : 256))); }
 
+// What the grouped form adds to a call (see GemmParams): `experts` matrices in w, row tiles of
+// `tile_rows` rows each, `max_tiles` of them launched.
+struct Grouped {
+  int experts, tile_rows, max_tiles;
+  const int* tile_expert;
+  const int* tile_row;
+  const int* offsets;
+};
+
 static int run_gemm(const void* x, const void* w, const float* bias, void* y, int n, int o, int k, int epilogue, int ksplit,
-                    float* ws_part, unsigned* ws_count, int* status, const QkvRope* rope, cudaStream_t stream) {
+                    float* ws_part, unsigned* ws_count, int* status, const QkvRope* rope, cudaStream_t stream,
+                    float act_limit = 0.f, float act_slope = 1.f, const Grouped* grouped = nullptr) {
   if (n <= 0 || o <= 0) return 0;
   if (k <= 0 || (k % 8) != 0) return FE_ERR_BAD_SHAPE;
-  if ((epilogue == EPI_SILU_MUL_BF16 || epilogue == EPI_GELU_MUL_BF16) && ((o % 32) != 0 || bias != nullptr)) return FE_ERR_BAD_SHAPE;
+  if (is_gated(epilogue) && ((o % 32) != 0 || bias != nullptr)) return FE_ERR_BAD_SHAPE;
   if ((((uintptr_t)x) | ((uintptr_t)w)) & 15) return FE_ERR_BAD_ALIGN;
   if (ksplit < 1) ksplit = 1;
   const int kblocks = (k + BK - 1) / BK;
   if (ksplit > kblocks) ksplit = kblocks;
-  const int bn = fe_gemm_tc5_tile(n);
+  const int bn = grouped ? grouped->tile_rows : fe_gemm_tc5_tile(n);
+  if (grouped && (ksplit != 1 || bias != nullptr || epilogue == EPI_QKV_ROPE || epilogue == EPI_ADD_F32)) return FE_ERR_BAD_SHAPE;
 
   CUtensorMap mw, mx;
-  int rc = make_map(&mw, w, o, k, BM);
+  int rc = make_map(&mw, w, grouped ? (long long)grouped->experts * o : o, k, BM);
   if (rc) return rc;
   rc = make_map(&mx, x, n, k, bn);
   if (rc) return rc;
@@ -607,8 +653,14 @@ static int run_gemm(const void* x, const void* w, const float* bias, void* y, in
     return FE_ERR_BAD_SHAPE;
   const int cluster_reduce = (!atomic_add && ksplit > 1 && ksplit <= 8 && bn <= CLUSTER_REDUCE_TOKENS) ? 1 : 0;
   GemmParams p{y, bias, n, o, k, epilogue, ksplit, cluster_reduce, atomic_add, ws_part, ws_count, status,
-               g_test_wait_limit ? g_test_wait_limit : WAIT_LIMIT, g_test_skip_kblock, rope ? *rope : QkvRope{}};
-  dim3 grid((o + BM - 1) / BM, (n + bn - 1) / bn, ksplit);
+               g_test_wait_limit ? g_test_wait_limit : WAIT_LIMIT, g_test_skip_kblock, rope ? *rope : QkvRope{},
+               act_limit, act_slope, nullptr, nullptr, nullptr};
+  if (grouped) {
+    p.g_expert = grouped->tile_expert;
+    p.g_row = grouped->tile_row;
+    p.g_offsets = grouped->offsets;
+  }
+  dim3 grid((o + BM - 1) / BM, grouped ? grouped->max_tiles : (n + bn - 1) / bn, ksplit);
   if (grid.y > 65535 || grid.z > 65535) return FE_ERR_TOO_LARGE;
   switch (bn) {
     case 16: return launch_bn<16>(mw, mx, p, grid, stream);
@@ -624,11 +676,28 @@ static int run_gemm(const void* x, const void* w, const float* bias, void* y, in
 // 5 the same with the tanh form of GELU in place of SiLU.
 // ksplit > 1 needs ws_part (floats: feature tiles * token tiles * ksplit * tile * 128) and
 // ws_count (one zeroed unsigned per output tile; left zeroed).
+// 6: y[n, o/2] = g' sigmoid(act_slope g') (u' + 1) with g' = min(gate, act_limit), u' = clamp(up, +-act_limit).
 FE_EXPORT int fe_gemm_tc5(const void* x, const void* w, const float* bias, void* y, int n, int o, int k,
                           int epilogue, int ksplit, float* ws_part, unsigned* ws_count, int* status,
-                          cudaStream_t stream) {
-  if ((epilogue < EPI_STORE_BF16 || epilogue > EPI_SILU_MUL_BF16) && epilogue != EPI_GELU_MUL_BF16) return FE_ERR_BAD_DTYPE;
-  return run_gemm(x, w, bias, y, n, o, k, epilogue, ksplit, ws_part, ws_count, status, nullptr, stream);
+                          float act_limit, float act_slope, cudaStream_t stream) {
+  if ((epilogue < EPI_STORE_BF16 || epilogue > EPI_SILU_MUL_BF16) && epilogue != EPI_GELU_MUL_BF16 && epilogue != EPI_CLAMP_MUL_BF16)
+    return FE_ERR_BAD_DTYPE;
+  return run_gemm(x, w, bias, y, n, o, k, epilogue, ksplit, ws_part, ws_count, status, nullptr, stream, act_limit, act_slope);
+}
+
+// The grouped form: x [slots, k] holds rows sorted by expert, w [experts, o, k]; row tile t
+// (of max_tiles; tile_rows = 16, 32, 64 or 128 rows, as the table was made) belongs to expert
+// tile_expert[t] (negative: unused) and starts at row tile_row[t]; expert e's rows end before
+// offsets[e + 1].  y [slots, o] (epilogues 0, 1) or [slots, o / 2] (3, 5, 6), rows as in x.
+FE_EXPORT int fe_gemm_tc5_grouped(const void* x, const void* w, void* y, int slots, int experts, int o, int k, int epilogue,
+                                  int tile_rows, int max_tiles, const int* tile_expert, const int* tile_row,
+                                  const int* offsets, float act_limit, float act_slope, int* status, cudaStream_t stream) {
+  if (epilogue != EPI_STORE_BF16 && epilogue != EPI_STORE_F32 && !is_gated(epilogue)) return FE_ERR_BAD_DTYPE;
+  if (tile_rows != 16 && tile_rows != 32 && tile_rows != 64 && tile_rows != 128) return FE_ERR_BAD_SHAPE;
+  if (experts < 1 || max_tiles < 1 || max_tiles > 65535 || (long long)experts * o > 0x7fffffffLL) return FE_ERR_BAD_SHAPE;
+  const Grouped grouped{experts, tile_rows, max_tiles, tile_expert, tile_row, offsets};
+  return run_gemm(x, w, nullptr, y, slots, o, k, epilogue, 1, nullptr, nullptr, status, nullptr, stream, act_limit, act_slope,
+                  &grouped);
 }
 
 // The fused q/k/v projection of up to 64 tokens with 128-wide heads: y [n, (nq + 2 nkv) * 128]

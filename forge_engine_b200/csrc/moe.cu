@@ -101,7 +101,7 @@ moe_route_kernel(const float* __restrict__ logits, long long ld, int n_tokens, i
 // plan
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(1024)
-moe_plan_kernel(int* __restrict__ counts, int experts, int slots, int max_tiles, const int* __restrict__ slot_expert,
+moe_plan_kernel(int* __restrict__ counts, int experts, int slots, int max_tiles, int tile_rows, const int* __restrict__ slot_expert,
                 const int* __restrict__ slot_rank, int* __restrict__ offsets, int* __restrict__ tile_expert,
                 int* __restrict__ tile_row, int* __restrict__ slot_row, int* __restrict__ row_slot) {
   extern __shared__ int start[];      // [experts + 1]
@@ -112,7 +112,7 @@ moe_plan_kernel(int* __restrict__ counts, int experts, int slots, int max_tiles,
     for (int e = 0; e < experts; ++e) {
       start[e] = at;
       const int count = counts[e];
-      for (int r = 0; r < count && tile < max_tiles; r += MOE_BM, ++tile) {
+      for (int r = 0; r < count && tile < max_tiles; r += tile_rows, ++tile) {
         tile_expert[tile] = e;
         tile_row[tile] = at + r;
       }
@@ -129,6 +129,47 @@ moe_plan_kernel(int* __restrict__ counts, int experts, int slots, int max_tiles,
     slot_row[s] = row;
     row_slot[row] = s;
   }
+}
+
+// ---------------------------------------------------------------------------
+// gather: sorted row r = the activations of its slot's token, times the slot's weight where
+// the weight scales the expert's input (32-bit product, one rounding).  For the products that
+// fetch their operands by TMA and so need the rows side by side.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_gather_kernel(const T* __restrict__ x, int width, int top, const int* __restrict__ row_slot,
+                  const float* __restrict__ slot_weight, T* __restrict__ out) {
+  pdl_trigger();
+  pdl_wait();
+  const int row = blockIdx.x;
+  const int slot = row_slot[row];
+  const float scale = slot_weight ? slot_weight[slot] : 1.f;
+  const T* src = x + (size_t)(slot / top) * width;
+  T* dst = out + (size_t)row * width;
+  if ((width & 7) == 0) {
+    for (int i = threadIdx.x * 8; i < width; i += blockDim.x * 8) {
+      float v[8];
+      load8(src + i, v);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] *= scale;
+      store8(dst + i, v);
+    }
+  } else {
+    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = from_float<T>(to_float(src[i]) * scale);
+  }
+}
+
+FE_EXPORT int fe_moe_gather(const void* x, int dtype, int width, int top, int slots, const int* row_slot,
+                            const float* slot_weight, void* out, cudaStream_t stream) {
+  if (slots <= 0) return 0;
+  int rc;
+  if (dtype == FE_DTYPE_BF16)
+    rc = fe_launch_dependent(moe_gather_kernel<bf16>, dim3(slots), dim3(256), 0, stream, (const bf16*)x, width, top, row_slot, slot_weight, (bf16*)out);
+  else if (dtype == FE_DTYPE_F32)
+    rc = fe_launch_dependent(moe_gather_kernel<float>, dim3(slots), dim3(256), 0, stream, (const float*)x, width, top, row_slot, slot_weight, (float*)out);
+  else return FE_ERR_BAD_DTYPE;
+  return rc ? rc : fe_last_error();
 }
 
 // ---------------------------------------------------------------------------
@@ -394,8 +435,11 @@ moe_combine_kernel(const float* __restrict__ rows, const int* __restrict__ slot_
 // ---------------------------------------------------------------------------
 // launchers
 // ---------------------------------------------------------------------------
-FE_EXPORT int fe_moe_max_tiles(int slots, int experts) {
-  return (slots + MOE_BM - 1) / MOE_BM + (experts < slots ? experts : slots);
+// Row tiles to launch for `slots` rows spread over `experts` in tiles of `tile_rows` rows
+// (0: the 64 of this file's own products): every expert may end with a tile that is not full.
+FE_EXPORT int fe_moe_max_tiles(int slots, int experts, int tile_rows) {
+  if (tile_rows <= 0) tile_rows = MOE_BM;
+  return (slots + tile_rows - 1) / tile_rows + (experts < slots ? experts : slots);
 }
 
 // logits [tokens, ld] (the first `experts` columns); counts [experts] must be zero and is zero
@@ -403,7 +447,8 @@ FE_EXPORT int fe_moe_max_tiles(int slots, int experts) {
 FE_EXPORT int fe_moe_route(const float* logits, long long ld, int n_tokens, int experts, int top, int softmax_scores,
                            int renormalise, int* counts, int* slot_expert, float* slot_weight, int* slot_rank,
                            int* slot_row, int* row_slot, int* offsets, int* tile_expert, int* tile_row, int max_tiles,
-                           cudaStream_t stream) {
+                           int tile_rows, cudaStream_t stream) {
+  if (tile_rows <= 0) tile_rows = MOE_BM;
   if (n_tokens <= 0) return 0;
   if (experts < 1 || top < 1 || top > experts || top > MOE_MAX_TOP || ld < experts) return FE_ERR_BAD_SHAPE;
   if ((long long)n_tokens * top > 0x7fffffffLL) return FE_ERR_TOO_LARGE;
@@ -413,7 +458,7 @@ FE_EXPORT int fe_moe_route(const float* logits, long long ld, int n_tokens, int 
   if (rc) return rc;
   const size_t smem = (size_t)(experts + 1) * sizeof(int);
   if (smem > 48 * 1024) cudaFuncSetAttribute(moe_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  rc = fe_launch_dependent(moe_plan_kernel, dim3(1), dim3(1024), smem, stream, counts, experts, n_tokens * top, max_tiles,
+  rc = fe_launch_dependent(moe_plan_kernel, dim3(1), dim3(1024), smem, stream, counts, experts, n_tokens * top, max_tiles, tile_rows,
                            (const int*)slot_expert, (const int*)slot_rank, offsets, tile_expert, tile_row, slot_row, row_slot);
   return rc ? rc : fe_last_error();
 }

@@ -65,10 +65,10 @@ def _declare(handle: ctypes.CDLL) -> None:
         "fe_attention_general": [p, ll, ll, p, i, i, p, i, i, p, ll, ll, i, p, i, i, i, i, i, p, p, p, i, f,
                                  i, f, f, i, i, ll, i, ll, p, ll, i, i, p, p],
         "fe_differential_combine": [p, p, i, ll, i, f, f, f, p],
-        "fe_moe_route": [p, ll, i, i, i, i, i, p, p, p, p, p, p, p, p, p, i, p],
+        "fe_moe_route": [p, ll, i, i, i, i, i, p, p, p, p, p, p, p, p, p, i, i, p],
         "fe_moe_grouped": [p, i, ll, p, p, i, p, i, i, i, i, i, p, p, p, p, p, i, f, f, i, p],
         "fe_moe_combine": [p, p, p, i, i, p, i, p, ll, p, i, i, p],
-        "fe_moe_max_tiles": [i, i],
+        "fe_moe_max_tiles": [i, i, i],
         "fe_linear_recurrence": [p, i, i, i, i, i, i, p, p, p, p, p, i, i, i, i, i, p],
         "fe_linear_recurrence_chunked": [p, i, i, i, i, i, i, p, p, p, p, p, p, i, i, i, i, i, i, p],
         "fe_linear_recurrence_chunks": [i, i],
@@ -81,7 +81,9 @@ def _declare(handle: ctypes.CDLL) -> None:
         "fe_attention_simt": [p, i, i, p, p, p, i, i, i, p, p, i, f, p, i, i, i, i, p, p],
         "fe_gemm_simt": [p, i, p, i, p, p, i, i, i, i, i, p],
         "fe_sample": [p, i, i, p, p, p, p, p, p, p, p, p],
-        "fe_gemm_tc5": [p, p, p, p, i, i, i, i, i, p, p, p, p],
+        "fe_gemm_tc5": [p, p, p, p, i, i, i, i, i, p, p, p, f, f, p],
+        "fe_gemm_tc5_grouped": [p, p, p, i, i, i, i, i, i, i, p, p, p, f, f, p, p],
+        "fe_moe_gather": [p, i, i, i, i, p, p, p, p],
         "fe_gemm_tc5_qkv_rope": [p, p, p, p, i, i, i, p, p, f, p, p, p, p, p, p, i, i, i, i, i, i, p, p],
     }
     for name, argtypes in signatures.items():
@@ -332,13 +334,42 @@ def differential_combine(maps: torch.Tensor, out: torch.Tensor, value_dim: int, 
                                         float(lam), float(eps), float(mult), stream()), "differential_combine")
 
 
-def moe_max_tiles(slots: int, experts: int) -> int:
-    """Row tiles the grouped products are launched with for ``slots`` (token, choice) pairs."""
-    return int(lib().fe_moe_max_tiles(int(slots), int(experts)))
+def moe_max_tiles(slots: int, experts: int, tile_rows: int = 0) -> int:
+    """Row tiles the grouped products are launched with for ``slots`` (token, choice) pairs cut
+    into tiles of ``tile_rows`` rows (0: the 64 of the plain grouped kernels)."""
+    return int(lib().fe_moe_max_tiles(int(slots), int(experts), int(tile_rows)))
+
+
+def moe_gather(x: torch.Tensor, plan: dict, top: int, slot_weight: torch.Tensor | None, out: torch.Tensor) -> None:
+    """out[row] = x[token of the row's slot] (times the slot's weight), rows sorted by expert."""
+    _dense(x, "x"), _dense(out, "out")
+    slots, width = out.shape
+    assert x.shape[1] == width and out.dtype == x.dtype and slots == x.shape[0] * top
+    check(lib().fe_moe_gather(ptr(x), code(x), int(width), int(top), int(slots), ptr(plan["row_slot"]), ptr(slot_weight),
+                              ptr(out), stream()), "moe_gather")
+
+
+def gemm_tc5_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, plan: dict, tile_rows: int,
+                     max_tiles: int, status: torch.Tensor, limit: float = 0.0, slope: float = 1.0) -> None:
+    """The tcgen05 product over rows sorted by expert: ``x`` [slots, k], ``w`` [experts, o, k],
+    ``out`` [slots, o] (epilogue 0: bfloat16, 1: 32-bit) or [slots, o / 2] (the gated
+    epilogues, for ``w`` whose rows alternate 16 gate and 16 up features).  ``plan`` is what
+    ``moe_route`` made with the same ``tile_rows`` and ``max_tiles``."""
+    _dense(x, "x"), _dense(w, "w"), _dense(out, "out")
+    slots, k = x.shape
+    experts, o, _ = w.shape
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[2] == k and k % 8 == 0
+    gated = epilogue in (TC5_SILU_MUL, TC5_GELU_MUL, TC5_CLAMP_MUL)
+    assert out.shape == (slots, o // 2 if gated else o)
+    assert out.dtype == (torch.float32 if epilogue == TC5_STORE_F32 else torch.bfloat16)
+    check(lib().fe_gemm_tc5_grouped(ptr(x), ptr(w), ptr(out), int(slots), int(experts), int(o), int(k), int(epilogue),
+                                    int(tile_rows), int(max_tiles), ptr(plan["tile_expert"]), ptr(plan["tile_row"]),
+                                    ptr(plan["offsets"]), float(limit), float(slope), ptr(status), stream()),
+          "gemm_tc5_grouped")
 
 
 def moe_route(logits: torch.Tensor, experts: int, top: int, softmax: bool, renormalise: bool, counts: torch.Tensor,
-              ints: torch.Tensor, slot_weight: torch.Tensor, max_tiles: int) -> dict:
+              ints: torch.Tensor, slot_weight: torch.Tensor, max_tiles: int, tile_rows: int = 0) -> dict:
     """Choose ``top`` of ``experts`` per token from 32-bit ``logits`` [N, >= experts] and lay
     the (token, choice) slots out by expert.  ``counts`` int32 [experts] must be zero (it is
     zero again afterwards); ``ints`` is int32 scratch of at least 4 * N * top + experts + 1 +
@@ -359,7 +390,7 @@ def moe_route(logits: torch.Tensor, experts: int, top: int, softmax: bool, renor
                              int(top), 1 if softmax else 0, 1 if renormalise else 0, ptr(counts),
                              ptr(views["slot_expert"]), ptr(slot_weight), ptr(views["slot_rank"]), ptr(views["slot_row"]),
                              ptr(views["row_slot"]), ptr(views["offsets"]), ptr(views["tile_expert"]),
-                             ptr(views["tile_row"]), int(max_tiles), stream()), "moe_route")
+                             ptr(views["tile_row"]), int(max_tiles), int(tile_rows), stream()), "moe_route")
     global LAUNCHES
     LAUNCHES += 1
     return views
@@ -972,6 +1003,8 @@ def gemm_simt(
 
 TC5_STORE_BF16, TC5_STORE_F32, TC5_ADD_F32, TC5_SILU_MUL = 0, 1, 2, 3
 TC5_GELU_MUL = 5      # the gated epilogue with the tanh form of GELU
+TC5_CLAMP_MUL = 6     # the gated epilogue with the clamped unit g' sigmoid(slope g') (u' + 1)
+TC5_GATED = {0: 3, 1: 5, 2: 6}      # activation code (ACT_*) -> gated epilogue
 
 
 def tc5_tile(n: int) -> int:
@@ -1054,18 +1087,19 @@ def tc5_ksplit(o: int, k: int) -> int:
 
 
 def gemm_tc5(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, status: torch.Tensor,
-             bias: torch.Tensor | None = None, ksplit: int = 1) -> None:
+             bias: torch.Tensor | None = None, ksplit: int = 1, limit: float = 0.0, slope: float = 1.0) -> None:
     """out = x @ w.T on tcgen05 tensor cores (bfloat16 operands, TMA-fed).
 
     epilogue 0: out bf16 [n, o]; 1: out f32 [n, o]; 2: out f32 [n, o] += product;
     3: out bf16 [n, o/2] = silu(gate) * up for w whose rows alternate 16 gate, 16 up features
-    (5: the same with the tanh form of GELU).
+    (5: the same with the tanh form of GELU; 6: g' sigmoid(slope g') (u' + 1) with g' = min(gate,
+    limit), u' = clamp(up, -limit, limit)).
     ``ksplit`` blocks share an output tile (deterministic reduction through a workspace)."""
     _dense(x, "x"), _dense(w, "w"), _dense(out, "out")
     n, k = x.shape
     o = w.shape[0]
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == k
-    if epilogue in (TC5_SILU_MUL, TC5_GELU_MUL):
+    if epilogue in (TC5_SILU_MUL, TC5_GELU_MUL, TC5_CLAMP_MUL):
         assert out.shape == (n, o // 2) and out.dtype == torch.bfloat16
     else:
         assert out.shape == (n, o)
@@ -1078,7 +1112,7 @@ def gemm_tc5(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int,
         tiles = -(-o // 128) * -(-n // tile_n)
         part, count = _tc5_workspace(x.device, tiles, ksplit, tile_n)
     check(lib().fe_gemm_tc5(ptr(x), ptr(w), ptr(bias), ptr(out), n, o, k, int(epilogue), ksplit, ptr(part),
-                            ptr(count), ptr(status), stream()),
+                            ptr(count), ptr(status), float(limit), float(slope), stream()),
           "gemm_tc5")
 
 

@@ -66,7 +66,7 @@ class PreNormBlock:
             usable = (self.ctx.dtype == torch.bfloat16 and hasattr(self.mixer, "attend")
                       and all(lin is not None and lin.bias is None and lin.weight.dtype == torch.bfloat16
                               for lin in (o_proj, gate_up, down))
-                      and getattr(self.ffn, "block", 0) == 16
+                      and getattr(self.ffn, "block", 0) == 16 and getattr(self.ffn, "activation", None) == native.ACT_SILU
                       and hasattr(norm, "eps") and getattr(norm, "weight", None) is not None
                       and os.environ.get("FORGE_ENGINE_DECODE_CHAIN", "0") == "1")
             if usable:

@@ -53,14 +53,14 @@ class GatedMLP(FeedForward):
     def forward_add(self, x, residual) -> bool:
         """``forward`` with the update added into the 32-bit ``residual`` by the down projection
         itself.  False (and nothing done) where that projection cannot."""
-        if not (self.block == 16 and self.activation == native.ACT_SILU and self.down.adds_into(x, residual) and self.gate_up._tc5_ok(x)
+        if not (self.block == 16 and self.activation in (native.ACT_SILU, native.ACT_CLAMPED_SWISH)
+                and self.down.adds_into(x, residual) and self.gate_up._tc5_ok(x)
                 and self.gate_up.out_features % 32 == 0 and self.gate_up.bias is None):
             return False
-        return self.down.add_into(self.gate_up.silu_mul(x, self.block), residual)
+        return self.down.add_into(self.gate_up.silu_mul(x, self.block, self.activation, self.limit, self.slope), residual)
 
     def forward(self, x):
-        fused = self.block and self.activation in (native.ACT_SILU, native.ACT_GELU_TANH)
-        act = self.gate_up.silu_mul(x, self.block, self.activation) if fused else None
+        act = self.gate_up.silu_mul(x, self.block, self.activation, self.limit, self.slope) if self.block else None
         if act is None:
             act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
             if self.activation == native.ACT_SILU:

@@ -81,16 +81,17 @@ class Linear:
                         ksplit=native.tc5_ksplit_add(self.out_features, self.in_features))
         return True
 
-    def silu_mul(self, x: torch.Tensor, interleave: int, act: int = native.ACT_SILU) -> torch.Tensor | None:
+    def silu_mul(self, x: torch.Tensor, interleave: int, act: int = native.ACT_SILU, limit: float = 0.0,
+                 slope: float = 1.0) -> torch.Tensor | None:
         """For a weight whose rows alternate ``interleave`` gate and up features: returns
-        act(gate) * up [n, out/2] from the fused tcgen05 epilogue (SiLU, or the tanh form of
-        GELU), or None if that kernel does not take this call (then the caller multiplies after
-        a plain product)."""
+        act(gate) * up [n, out/2] from the fused tcgen05 epilogue (SiLU, the tanh form of
+        GELU, or the clamped unit with ``limit`` and ``slope``), or None if that kernel does
+        not take this call (then the caller multiplies after a plain product)."""
         if interleave != 16 or not self._tc5_ok(x) or self.out_features % 32 or self.bias is not None:
             return None
         out = torch.empty((x.shape[0], self.out_features // 2), dtype=torch.bfloat16, device=x.device)
-        native.gemm_tc5(x, self.weight, out, native.TC5_SILU_MUL if act == native.ACT_SILU else native.TC5_GELU_MUL, self.status,
-                        ksplit=native.tc5_ksplit(self.out_features, self.in_features))
+        native.gemm_tc5(x, self.weight, out, native.TC5_GATED[act], self.status,
+                        ksplit=native.tc5_ksplit(self.out_features, self.in_features), limit=limit, slope=slope)
         return out
 
 

@@ -10,6 +10,8 @@ step replays from a CUDA graph.
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..config.specs import local_name
@@ -19,6 +21,7 @@ from .base import BuildContext, FeedForward, WeightInfo, build_part, part_class,
 from .ffn import ACTIVATIONS
 
 MAX_TOP = 32
+INTERLEAVE = 16       # gate and up features alternate in sixteens in the fused matrix
 
 
 def _shared_spec(spec):
@@ -60,6 +63,10 @@ class RoutedMLP(FeedForward):
         self.router = torch.cat([r.float() for r in rows], dim=0).contiguous()
         del rows
         names = [local_name(unit, n) for n in ("gate_proj.weight", "up_proj.weight", "down_proj.weight")]
+        # bfloat16 with sizes in sixteens: the products run on the tcgen05 kernel in its grouped
+        # form, gate and up as one matrix per expert whose rows alternate 16 gate and 16 up features
+        self.fused = (ctx.dtype == torch.bfloat16 and self.width % 8 == 0 and self.inter % INTERLEAVE == 0
+                      and os.environ.get("FORGE_ENGINE_MOE_TC5", "1") != "0")
         stacks = []
         for name, shape in zip(names, ((self.inter, self.width), (self.inter, self.width), (self.width, self.inter))):
             stack = None
@@ -71,6 +78,16 @@ class RoutedMLP(FeedForward):
                 del tensor
             stacks.append(stack)
         self.gate, self.up, self.down = stacks
+        self.gate_up_stack = None
+        if self.fused and all(t.dtype == torch.bfloat16 for t in stacks):
+            blocks = self.inter // INTERLEAVE
+            self.gate_up_stack = torch.empty((self.experts, 2 * self.inter, self.width), dtype=torch.bfloat16, device=self.gate.device)
+            view = self.gate_up_stack.view(self.experts, blocks, 2, INTERLEAVE, self.width)
+            view[:, :, 0].copy_(self.gate.view(self.experts, blocks, INTERLEAVE, self.width))
+            view[:, :, 1].copy_(self.up.view(self.experts, blocks, INTERLEAVE, self.width))
+            self.gate = self.up = None
+        else:
+            self.fused = False
         if spec.shared is not None:
             self.shared = build_part(_shared_spec(spec), weights, ctx)
         self.counts = torch.zeros(self.experts, dtype=torch.int32, device=ctx.device)
@@ -91,24 +108,42 @@ class RoutedMLP(FeedForward):
                 shapes["shared.sg"] = WeightInfo((1, h))
         return shapes
 
+    def tile_rows(self, slots: int) -> int:
+        """Rows of a row tile of the tcgen05 products: few rows per expert (decoding) take
+        the narrow tiles, whose rings are deepest."""
+        wish = int(os.environ.get("FORGE_ENGINE_MOE_TILE", "0"))
+        if wish in (16, 32, 64, 128):
+            return wish
+        per_expert = slots / self.experts
+        return 16 if per_expert <= 16 else 32 if per_expert <= 32 else 64 if per_expert <= 96 else 128
+
     def forward(self, x):
         n = x.shape[0]
         slots = n * self.top
         device = x.device
         logits = torch.empty((n, self.router.shape[0]), dtype=torch.float32, device=device)
         native.gemm_simt(x, self.router, logits)
-        max_tiles = native.moe_max_tiles(slots, self.experts)
+        tile_rows = self.tile_rows(slots) if self.fused else 0
+        max_tiles = native.moe_max_tiles(slots, self.experts, tile_rows)
         ints = torch.empty(4 * slots + self.experts + 1 + 2 * max_tiles, dtype=torch.int32, device=device)
         weight = torch.empty(slots, dtype=torch.float32, device=device)
         self.counts.zero_()
         plan = native.moe_route(logits, self.experts, self.top, self.softmax, self.renormalise, self.counts, ints,
-                                weight, max_tiles)
+                                weight, max_tiles, tile_rows)
         hidden = torch.empty((slots, self.inter), dtype=x.dtype, device=device)
-        native.moe_grouped(x, self.gate, self.up, hidden, plan, self.top, max_tiles, gather=True,
-                           slot_weight=weight if self.weight_on_input else None, act=self.activation,
-                           limit=self.limit, slope=self.slope)
         rows = torch.empty((slots, self.width), dtype=torch.float32, device=device)
-        native.moe_grouped(hidden, self.down, None, rows, plan, self.top, max_tiles, gather=False)
+        if self.fused:
+            sorted_x = torch.empty((slots, self.width), dtype=x.dtype, device=device)
+            native.moe_gather(x, plan, self.top, weight if self.weight_on_input else None, sorted_x)
+            native.gemm_tc5_grouped(sorted_x, self.gate_up_stack, hidden, native.TC5_GATED[self.activation], plan, tile_rows,
+                                    max_tiles, self.ctx.status, self.limit, self.slope)
+            native.gemm_tc5_grouped(hidden, self.down, rows, native.TC5_STORE_F32, plan, tile_rows, max_tiles,
+                                    self.ctx.status)
+        else:
+            native.moe_grouped(x, self.gate, self.up, hidden, plan, self.top, max_tiles, gather=True,
+                               slot_weight=weight if self.weight_on_input else None, act=self.activation,
+                               limit=self.limit, slope=self.slope)
+            native.moe_grouped(hidden, self.down, None, rows, plan, self.top, max_tiles, gather=False)
         shared = None if self.shared is None else self.shared.forward(x)
         out = torch.empty((n, self.width), dtype=torch.float32, device=device)
         native.moe_combine(rows, plan, self.top, out, slot_weight=None if self.weight_on_input else weight,

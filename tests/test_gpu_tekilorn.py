@@ -95,7 +95,7 @@ def mixed_config(dtype: str = "float32"):
     margins are known (``test_routed_feed_forward_alone``)."""
     tops = (2, 1) if dtype == "float32" else (5, 5)
     return pt.config(
-        [pt.differential_layer(), pt.window_layer(window=6, keep_first=2, mlp=pt.routed(top=tops[0])),
+        [pt.differential_layer(), pt.window_layer(window=6, keep_first=2, mlp=pt.routed(top=tops[0], ff=32)),
          pt.window_layer(heads=2, kv_heads=1, dim=16, vdim=32, window=11, keep_first=5, rot_dims=16, mlp=pt.routed(top=tops[1])),
          pt.differential_layer(heads=2, kv_heads=2, dim=16, vdim=16, softcap=None, mlp=None)],
         loop=(1, 3, 2))
@@ -458,15 +458,18 @@ def test_differential_combine():
 
 
 @pytest.mark.parametrize("dtype", (torch.float32, torch.bfloat16))
-@pytest.mark.parametrize("experts, top, tokens", ((7, 2, 150), (3, 3, 5), (40, 1, 33), (6, 4, 1)))
-def test_routed_feed_forward_alone(experts, top, tokens, dtype):
+@pytest.mark.parametrize("experts, top, tokens, ff", ((7, 2, 150, 32), (3, 3, 5, 24), (40, 1, 33, 16), (6, 4, 1, 48),
+                                                      (4, 2, 700, 64), (5, 1, 300, 40)))
+def test_routed_feed_forward_alone(experts, top, tokens, ff, dtype):
     """The part alone against a loop over tokens and experts: the chosen experts, weights on
-    the input, the shared unit with its gate; router margins are made clear."""
+    the input, the shared unit with its gate; tokens whose router margin is not clear are left
+    out.  Widths in sixteens run the grouped tensor-core products in bfloat16 (few and many rows
+    per expert: narrow and wide row tiles), others the plain grouped kernels."""
     from forge_engine_b200.config.specs import GatedMLPSpec, RoutedMLPSpec
     from forge_engine_b200.parts.base import BuildContext, build_part
 
     gen = torch.Generator().manual_seed(experts)
-    width, ff, limit = 40, 24, 1.0
+    width, limit = 40, 1.0
     cfg = pt.config([pt.window_layer(mlp=pt.routed(experts, top, ff, limit, 16, 2.0))], width=width)
     weights = {name[len("l0.mlp."):]: t for name, t in pt.random_weights(cfg, 7).items() if name.startswith("l0.mlp.")}
     x = torch.randn(tokens, width, generator=gen).to(torch.bfloat16)
@@ -482,7 +485,9 @@ def test_routed_feed_forward_alone(experts, top, tokens, dtype):
     engine_dtype = dtype
     ctx = BuildContext(dtype=engine_dtype, device=torch.device("cuda"), status=torch.zeros(1, dtype=torch.int32, device="cuda"))
     part = build_part(spec, {k: v.to(engine_dtype).cuda() for k, v in weights.items()}, ctx)
+    assert part.fused == (dtype == torch.bfloat16 and ff % 16 == 0)
     got = part.forward(x.to(engine_dtype).cuda()).float().cpu()
+    assert int(ctx.status.item()) == 0
     tol = 1e-4 if dtype == torch.float32 else 3e-2
     assert float((got[clear] - want[clear]).abs().max()) <= tol * max(1.0, float(want.abs().max()))
     assert int(part.counts.abs().sum()) == 0       # left zero for the next call
