@@ -58,6 +58,9 @@ __device__ __forceinline__ float query_temperature(int pos, float coef, int ever
   return every > 0 ? 1.f + coef * logf((float)((pos + 1) / every + 1)) : 1.f;
 }
 __device__ __forceinline__ float sigmoidf(float x) { return 1.f / (1.f + expf(-x)); }
+// tanh as 1 - 2 / (1 + e^(2x)) on the fast exponential: the absolute error stays below 3e-7,
+// which is what a capped score (cap * tanh, the cap a few tens) needs; it saturates to +-1
+__device__ __forceinline__ float tanh_capped(float x) { return 1.f - __fdividef(2.f, 1.f + __expf(2.f * x)); }
 
 __device__ __forceinline__ unsigned smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 
@@ -244,7 +247,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(Params p, 
           const int h = c >> 1;
           const int key = kt * BN + j * 8 + pair * 2 + (c & 1);
           float sc = s[j][c] * row_scale[h];
-          if (capped) sc = cap2 * tanhf(sc);
+          if (capped) sc = cap2 * tanh_capped(sc);
           sc -= row_slope[h] * (float)(row_pos[h] - key);
           s[j][c] = sc;
           mx[h] = fmaxf(mx[h], sc);
@@ -260,7 +263,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(Params p, 
           const bool visible = row_live[h] && key <= row_pos[h] &&
                                (p.window <= 0 || key > row_pos[h] - p.window || key < sink_keys);
           float sc = s[j][c] * row_scale[h];
-          if (capped) sc = cap2 * tanhf(sc);
+          if (capped) sc = cap2 * tanh_capped(sc);
           sc = visible ? sc - row_slope[h] * (float)(row_pos[h] - key) : -INFINITY;
           s[j][c] = sc;
           mx[h] = fmaxf(mx[h], sc);

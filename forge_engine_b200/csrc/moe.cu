@@ -44,6 +44,59 @@ __device__ __forceinline__ float moe_act(float z, float u, const MoeAct& a) {
 }
 
 // ---------------------------------------------------------------------------
+// router logits: out[n, r] = sum_k x[n, k] * w[r, k] for a handful of rows r, in plain 32-bit
+// FMAs.  A block takes one token (its activations in shared memory as floats) and eight rows,
+// a warp one row: lanes stride over k, the 32 partial sums meet in a butterfly.  The order of
+// additions depends on k alone, so a token's logits do not depend on the batch.
+// ---------------------------------------------------------------------------
+template <typename TX>
+__global__ void __launch_bounds__(256)
+moe_logits_kernel(const TX* __restrict__ x, const float* __restrict__ w, float* __restrict__ out, int rows, int k) {
+  extern __shared__ float xs[];
+  pdl_trigger();
+  pdl_wait();
+  const int token = blockIdx.x;
+  const TX* src = x + (size_t)token * k;
+  for (int i = threadIdx.x; i < k; i += blockDim.x) xs[i] = to_float(src[i]);
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const float* wr = w + (size_t)row * k;
+  float sum = 0.f;
+  if ((k & 3) == 0) {
+    for (int i = lane * 4; i < k; i += 128) {
+      const float4 a = *reinterpret_cast<const float4*>(wr + i);
+      sum = fmaf(xs[i], a.x, sum);
+      sum = fmaf(xs[i + 1], a.y, sum);
+      sum = fmaf(xs[i + 2], a.z, sum);
+      sum = fmaf(xs[i + 3], a.w, sum);
+    }
+  } else {
+    for (int i = lane; i < k; i += 32) sum = fmaf(xs[i], wr[i], sum);
+  }
+  sum = warp_sum(sum);
+  if (lane == 0) out[(size_t)token * rows + row] = sum;
+}
+
+// x [n, k] (bfloat16 or 32-bit), w [rows, k] 32-bit, out [n, rows] 32-bit
+FE_EXPORT int fe_moe_logits(const void* x, int x_dtype, const float* w, float* out, int n, int rows, int k, cudaStream_t stream) {
+  if (n <= 0 || rows <= 0) return 0;
+  if (k <= 0 || (size_t)k * sizeof(float) > 200 * 1024 || ((uintptr_t)w & 15)) return FE_ERR_BAD_SHAPE;
+  const size_t smem = (size_t)k * sizeof(float);
+  dim3 grid(n, (rows + 7) / 8);
+  int rc;
+  if (x_dtype == FE_DTYPE_BF16) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(moe_logits_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    rc = fe_launch_dependent(moe_logits_kernel<bf16>, grid, dim3(256), smem, stream, (const bf16*)x, w, out, rows, k);
+  } else if (x_dtype == FE_DTYPE_F32) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(moe_logits_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    rc = fe_launch_dependent(moe_logits_kernel<float>, grid, dim3(256), smem, stream, (const float*)x, w, out, rows, k);
+  } else return FE_ERR_BAD_DTYPE;
+  return rc ? rc : fe_last_error();
+}
+
+// ---------------------------------------------------------------------------
 // route
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(128)
@@ -420,6 +473,28 @@ moe_combine_kernel(const float* __restrict__ rows, const int* __restrict__ slot_
   const int token = blockIdx.x;
   float gate = 0.f;
   if (shared != nullptr) gate = shared_logit ? 1.f / (1.f + expf(-shared_logit[(size_t)token * shared_ld])) : 1.f;
+  if ((width & 3) == 0) {
+    // four neighbouring columns per thread: 16-byte loads of the rows
+    for (int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4; c < width; c += gridDim.y * blockDim.x * 4) {
+      float sum[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int k = 0; k < top; ++k) {
+        const int slot = token * top + k;
+        float v[4];
+        load4(rows + (size_t)slot_row[slot] * width + c, v);
+        const float w = slot_weight ? slot_weight[slot] : 1.f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sum[e] += slot_weight ? v[e] * w : v[e];
+      }
+      if (shared != nullptr) {
+        float v[4];
+        load4(shared + (size_t)token * width + c, v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sum[e] = fmaf(gate, v[e], sum[e]);
+      }
+      store4(out + (size_t)token * width + c, sum);
+    }
+    return;
+  }
   for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < width; c += gridDim.y * blockDim.x) {
     float sum = 0.f;
     for (int k = 0; k < top; ++k) {
@@ -503,7 +578,7 @@ FE_EXPORT int fe_moe_combine(const float* rows, const int* slot_row, const float
                              const void* shared, int shared_dtype, const float* shared_logit, long long shared_ld,
                              void* out, int out_dtype, int n_tokens, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
-  int pieces = (width + 255) / 256;
+  int pieces = (width & 3) == 0 ? (width / 4 + 255) / 256 : (width + 255) / 256;
   if (pieces > 32) pieces = 32;
   dim3 grid(n_tokens, pieces);
   int rc = FE_ERR_BAD_DTYPE;

@@ -84,6 +84,7 @@ def _declare(handle: ctypes.CDLL) -> None:
         "fe_gemm_tc5": [p, p, p, p, i, i, i, i, i, p, p, p, f, f, p],
         "fe_gemm_tc5_grouped": [p, p, p, i, i, i, i, i, i, i, p, p, p, f, f, p, p],
         "fe_moe_gather": [p, i, i, i, i, p, p, p, p],
+        "fe_moe_logits": [p, i, p, p, i, i, i, p],
         "fe_gemm_tc5_qkv_rope": [p, p, p, p, i, i, i, p, p, f, p, p, p, p, p, p, i, i, i, i, i, i, p, p],
     }
     for name, argtypes in signatures.items():
@@ -338,6 +339,15 @@ def moe_max_tiles(slots: int, experts: int, tile_rows: int = 0) -> int:
     """Row tiles the grouped products are launched with for ``slots`` (token, choice) pairs cut
     into tiles of ``tile_rows`` rows (0: the 64 of the plain grouped kernels)."""
     return int(lib().fe_moe_max_tiles(int(slots), int(experts), int(tile_rows)))
+
+
+def moe_logits(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[n, r] = x[n] . w[r] for a handful of 32-bit rows ``w`` (a router), in plain 32-bit
+    FMAs whatever the dtype of ``x``."""
+    _dense(x, "x"), _dense(w, "w"), _dense(out, "out")
+    n, k = x.shape
+    assert w.dtype == torch.float32 and out.dtype == torch.float32 and w.shape[1] == k and out.shape == (n, w.shape[0])
+    check(lib().fe_moe_logits(ptr(x), code(x), ptr(w), ptr(out), n, int(w.shape[0]), int(k), stream()), "moe_logits")
 
 
 def moe_gather(x: torch.Tensor, plan: dict, top: int, slot_weight: torch.Tensor | None, out: torch.Tensor) -> None:

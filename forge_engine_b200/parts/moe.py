@@ -121,33 +121,42 @@ class RoutedMLP(FeedForward):
         n = x.shape[0]
         slots = n * self.top
         device = x.device
-        logits = torch.empty((n, self.router.shape[0]), dtype=torch.float32, device=device)
-        native.gemm_simt(x, self.router, logits)
+        section = self.ctx.section
+        with section("ffn.router"):
+            logits = torch.empty((n, self.router.shape[0]), dtype=torch.float32, device=device)
+            if self.width <= 48 * 1024:
+                native.moe_logits(x, self.router, logits)
+            else:
+                native.gemm_simt(x, self.router, logits)
         tile_rows = self.tile_rows(slots) if self.fused else 0
         max_tiles = native.moe_max_tiles(slots, self.experts, tile_rows)
-        ints = torch.empty(4 * slots + self.experts + 1 + 2 * max_tiles, dtype=torch.int32, device=device)
-        weight = torch.empty(slots, dtype=torch.float32, device=device)
-        self.counts.zero_()
-        plan = native.moe_route(logits, self.experts, self.top, self.softmax, self.renormalise, self.counts, ints,
-                                weight, max_tiles, tile_rows)
+        with section("ffn.route"):
+            ints = torch.empty(4 * slots + self.experts + 1 + 2 * max_tiles, dtype=torch.int32, device=device)
+            weight = torch.empty(slots, dtype=torch.float32, device=device)
+            self.counts.zero_()
+            plan = native.moe_route(logits, self.experts, self.top, self.softmax, self.renormalise, self.counts, ints,
+                                    weight, max_tiles, tile_rows)
         hidden = torch.empty((slots, self.inter), dtype=x.dtype, device=device)
         rows = torch.empty((slots, self.width), dtype=torch.float32, device=device)
-        if self.fused:
-            sorted_x = torch.empty((slots, self.width), dtype=x.dtype, device=device)
-            native.moe_gather(x, plan, self.top, weight if self.weight_on_input else None, sorted_x)
-            native.gemm_tc5_grouped(sorted_x, self.gate_up_stack, hidden, native.TC5_GATED[self.activation], plan, tile_rows,
-                                    max_tiles, self.ctx.status, self.limit, self.slope)
-            native.gemm_tc5_grouped(hidden, self.down, rows, native.TC5_STORE_F32, plan, tile_rows, max_tiles,
-                                    self.ctx.status)
-        else:
-            native.moe_grouped(x, self.gate, self.up, hidden, plan, self.top, max_tiles, gather=True,
-                               slot_weight=weight if self.weight_on_input else None, act=self.activation,
-                               limit=self.limit, slope=self.slope)
-            native.moe_grouped(hidden, self.down, None, rows, plan, self.top, max_tiles, gather=False)
-        shared = None if self.shared is None else self.shared.forward(x)
-        out = torch.empty((n, self.width), dtype=torch.float32, device=device)
-        native.moe_combine(rows, plan, self.top, out, slot_weight=None if self.weight_on_input else weight,
-                           shared=shared, shared_logit=logits[:, self.experts] if self.shared_gate else None)
+        with section("ffn.experts"):
+            if self.fused:
+                sorted_x = torch.empty((slots, self.width), dtype=x.dtype, device=device)
+                native.moe_gather(x, plan, self.top, weight if self.weight_on_input else None, sorted_x)
+                native.gemm_tc5_grouped(sorted_x, self.gate_up_stack, hidden, native.TC5_GATED[self.activation], plan,
+                                        tile_rows, max_tiles, self.ctx.status, self.limit, self.slope)
+                native.gemm_tc5_grouped(hidden, self.down, rows, native.TC5_STORE_F32, plan, tile_rows, max_tiles,
+                                        self.ctx.status)
+            else:
+                native.moe_grouped(x, self.gate, self.up, hidden, plan, self.top, max_tiles, gather=True,
+                                   slot_weight=weight if self.weight_on_input else None, act=self.activation,
+                                   limit=self.limit, slope=self.slope)
+                native.moe_grouped(hidden, self.down, None, rows, plan, self.top, max_tiles, gather=False)
+        with section("ffn.shared"):
+            shared = None if self.shared is None else self.shared.forward(x)
+        with section("ffn.combine"):
+            out = torch.empty((n, self.width), dtype=torch.float32, device=device)
+            native.moe_combine(rows, plan, self.top, out, slot_weight=None if self.weight_on_input else weight,
+                               shared=shared, shared_logit=logits[:, self.experts] if self.shared_gate else None)
         return out
 
 
