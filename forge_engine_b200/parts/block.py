@@ -82,24 +82,16 @@ class PreNormBlock:
         None; ``shift`` None or a 32-bit vector that is added to every row of ``h`` before
         anything else (in the first norm's kernel).  Returns this block's last update, still
         to be added (None when it has already been added)."""
-        if shift is not None or self.ffn is None:
-            with self.ctx.section("input_norm"):
-                normed = self.input_norm.add_forward(h, pending, shift=shift) if shift is not None \
-                    else self.input_norm.add_forward(h, pending)
-            with self.ctx.section("mixer"):
-                update = self.mixer.forward(normed, batch, cache)
-            if self.ffn is None:
-                return update
-            with self.ctx.section("post_norm"):
-                normed = self.post_norm.add_forward(h, update)
-            with self.ctx.section("ffn"):
-                return self.ffn.forward(normed)
-        chain = self._chain() if batch.n_tokens <= native.CHAIN_MAX_TOKENS and self.ctx.timer is None else None
+        enter = (lambda: self.input_norm.add_forward(h, pending)) if shift is None else \
+            (lambda: self.input_norm.add_forward(h, pending, shift=shift))
+        chain = None
+        if shift is None and self.ffn is not None and batch.n_tokens <= native.CHAIN_MAX_TOKENS and self.ctx.timer is None:
+            chain = self._chain()
         if chain is not None:
             # few tokens: output projection (+= h), norm + gate/up with SiLU*mul and the down
             # projection (+= h) run as one persistent kernel whose weight stream never stops
             o_proj, norm, gate_up, down = chain
-            normed = self.input_norm.add_forward(h, pending)
+            normed = enter()
             heads = self.mixer.attend(normed, batch, cache)
             act = torch.empty((h.shape[0], gate_up.out_features // 2), dtype=torch.bfloat16, device=h.device)
             native.decode_chain(
@@ -112,16 +104,20 @@ class PreNormBlock:
         if self.ctx.timer is None:
             # a part that can add its update into the residual stream itself (in the epilogue of
             # its last projection) does so; the norm after it then only reads the stream
-            normed = self.input_norm.add_forward(h, pending)
+            normed = enter()
             adds = getattr(self.mixer, "forward_add", None)
             update = None if adds is not None and adds(normed, batch, cache, h) else self.mixer.forward(normed, batch, cache)
+            if self.ffn is None:
+                return update
             normed = self.post_norm.add_forward(h, update)
             adds = getattr(self.ffn, "forward_add", None)
             return None if adds is not None and adds(normed, h) else self.ffn.forward(normed)
         with self.ctx.section("input_norm"):
-            normed = self.input_norm.add_forward(h, pending)
+            normed = enter()
         with self.ctx.section("mixer"):
             update = self.mixer.forward(normed, batch, cache)
+        if self.ffn is None:
+            return update
         with self.ctx.section("post_norm"):
             normed = self.post_norm.add_forward(h, update)
         with self.ctx.section("ffn"):

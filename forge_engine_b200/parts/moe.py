@@ -77,7 +77,7 @@ class RoutedMLP(FeedForward):
                 stack[e].copy_(tensor)
                 del tensor
             stacks.append(stack)
-        self.gate, self.up, self.down = stacks
+        self.gate, self.up, self.down_stack = stacks
         self.gate_up_stack = None
         if self.fused and all(t.dtype == torch.bfloat16 for t in stacks):
             blocks = self.inter // INTERLEAVE
@@ -144,13 +144,13 @@ class RoutedMLP(FeedForward):
                 native.moe_gather(x, plan, self.top, weight if self.weight_on_input else None, sorted_x)
                 native.gemm_tc5_grouped(sorted_x, self.gate_up_stack, hidden, native.TC5_GATED[self.activation], plan,
                                         tile_rows, max_tiles, self.ctx.status, self.limit, self.slope)
-                native.gemm_tc5_grouped(hidden, self.down, rows, native.TC5_STORE_F32, plan, tile_rows, max_tiles,
+                native.gemm_tc5_grouped(hidden, self.down_stack, rows, native.TC5_STORE_F32, plan, tile_rows, max_tiles,
                                         self.ctx.status)
             else:
                 native.moe_grouped(x, self.gate, self.up, hidden, plan, self.top, max_tiles, gather=True,
                                    slot_weight=weight if self.weight_on_input else None, act=self.activation,
                                    limit=self.limit, slope=self.slope)
-                native.moe_grouped(hidden, self.down, None, rows, plan, self.top, max_tiles, gather=False)
+                native.moe_grouped(hidden, self.down_stack, None, rows, plan, self.top, max_tiles, gather=False)
         with section("ffn.shared"):
             shared = None if self.shared is None else self.shared.forward(x)
         with section("ffn.combine"):
