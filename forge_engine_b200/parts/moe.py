@@ -90,6 +90,8 @@ class RoutedMLP(FeedForward):
             self.fused = False
         if spec.shared is not None:
             self.shared = build_part(_shared_spec(spec), weights, ctx)
+        # rows per expert, counted by the route kernel; the plan kernel reads them and leaves
+        # zeros behind, so no launch is spent on clearing them
         self.counts = torch.zeros(self.experts, dtype=torch.int32, device=ctx.device)
 
     @classmethod
@@ -133,7 +135,6 @@ class RoutedMLP(FeedForward):
         with section("ffn.route"):
             ints = torch.empty(4 * slots + self.experts + 1 + 2 * max_tiles, dtype=torch.int32, device=device)
             weight = torch.empty(slots, dtype=torch.float32, device=device)
-            self.counts.zero_()
             plan = native.moe_route(logits, self.experts, self.top, self.softmax, self.renormalise, self.counts, ints,
                                     weight, max_tiles, tile_rows)
         hidden = torch.empty((slots, self.inter), dtype=x.dtype, device=device)
