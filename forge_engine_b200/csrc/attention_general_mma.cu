@@ -55,6 +55,7 @@ struct Params {
   int keep_first; float softcap, temp_coef; int temp_every;
   int parts; long long q_ps; int k_ps; long long o_ps;
   const float* gate; long long gate_stride; int out_f32;
+  int row_hi;      // above zero: entries with more rows (new tokens x heads per kv head) are left to another kernel
 };
 
 __device__ __forceinline__ float query_temperature(int pos, float coef, int every) {
@@ -113,7 +114,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(Params p, 
   const int start = p.starts[entry];
   const int rows_total = count * p.groups;
   const int row0 = tile * BM;
-  if (row0 >= rows_total) return;
+  if (row0 >= rows_total || (p.row_hi > 0 && rows_total > p.row_hi)) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int rw = warp & 3, vcol0 = (warp >> 2) * DVW;      // the warp's sixteen rows and first value column
   const int* table = p.table + (size_t)entry * p.max_pages;
@@ -381,7 +382,7 @@ __global__ void __launch_bounds__(128) attention_mma_merge_kernel(Params p) {
   const int t_begin = p.cu_tokens[entry];
   const int rows_total = (p.cu_tokens[entry + 1] - t_begin) * p.groups;
   const int first = tile * BM + piece * MERGE_ROWS;
-  if (first >= rows_total) return;
+  if (first >= rows_total || (p.row_hi > 0 && rows_total > p.row_hi)) return;
   const float* base = p.part + (((size_t)entry * p.tiles + tile) * (p.nkv * p.parts) + blockIdx.z) * p.splits * (size_t)BM * (DV + 2);
   const int rows = min(MERGE_ROWS, rows_total - first);
   {
@@ -431,7 +432,7 @@ FE_EXPORT int GM_NAME(fe_attention_gmma_)(const void* q, long long q_ts, long lo
                                           int max_new, const float* slopes, int window, float scale, int splits,
                                           float* workspace, int keep_first, float softcap, float temp_coef,
                                           int temp_every, int parts, long long q_ps, int k_ps, long long o_ps,
-                                          const float* gate, long long gate_stride, int out_f32, int* status,
+                                          const float* gate, long long gate_stride, int out_f32, int row_hi, int* status,
                                           cudaStream_t stream) {
   if (entries <= 0 || max_new <= 0) return 0;
   if (parts < 1) parts = 1;
@@ -447,7 +448,7 @@ FE_EXPORT int GM_NAME(fe_attention_gmma_)(const void* q, long long q_ts, long lo
   Params p{(const bf16*)q, q_ts, q_hs, (const bf16*)k_cache, k_row, (const bf16*)v_cache, v_row, out, o_ts, o_hs,
            block_table, max_pages, page_size, num_pages, nkv, groups, cu_tokens, starts, slopes, window, scale,
            splits, tiles, workspace, keep_first, softcap, temp_coef, temp_every, parts, q_ps, k_ps, o_ps, gate,
-           gate_stride, out_f32};
+           gate_stride, out_f32, row_hi};
   static bool configured = false;
   if (!configured) {
     const cudaError_t rc = cudaFuncSetAttribute(attention_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);

@@ -67,6 +67,12 @@ struct AttnParams {
   unsigned* ws_count;    // [entries, nkv] zeroed arrival counters, or null: a merge kernel follows
   int cluster_merge;     // 1: the splits of a pair form one cluster and combine through shared memory;
                          // 2: clusters of 8 splits do, and the clusters' results go through the workspace
+  // The tcgen05 prefill kernel only (off when zero / null): with a window, keys below
+  // keep_first stay visible to every query; row (token, head) of the output is multiplied by
+  // sigmoid(gate[token * gate_stride + head]).
+  int keep_first = 0;
+  const float* gate = nullptr;
+  long long gate_stride = 0;
 };
 
 __device__ __forceinline__ unsigned smem_addr(const void* p) {
@@ -1161,6 +1167,53 @@ FE_EXPORT int SYM(fe_attention_mma_d)(const void* q, int q_stride, void* out, co
 static __device__ __align__(256) float fe_noalloc_scratch[FE_NOALLOC_SCRATCH_FLOATS];
 
 #define FE_NOALLOC_MAX_DEVICES 64
+
+// The tcgen05 prefill kernel alone, for layers whose other entries another kernel serves:
+// entries with more than `row_lo` rows (new tokens x heads per kv head).  Beyond what
+// fe_attention_mma_d gives it: with a window, keys below `keep_first` stay visible; row
+// (token, head) of `out` is multiplied by sigmoid(gate[token * gate_stride + head]) (gate
+// null: no gate).  q rows are `q_stride` apart, out is [tokens, heads * D].  Returns
+// FE_ERR_BAD_SHAPE where the kernel's shapes do not hold (head size 64 or 128, heads per kv
+// head dividing 128, pages of 4 to 128 keys that divide 128).
+FE_EXPORT int SYM(fe_attention_prefill_tc5_d)(const void* q, int q_stride, void* out, const void* k_cache,
+                                              const void* v_cache, const int* block_table, int max_pages, int page_size,
+                                              int num_pages, int num_kv_heads, int groups, const int* cu_tokens,
+                                              const int* starts, int entries, int max_new, int total_tokens, int window,
+                                              int keep_first, float scale, const float* gate, long long gate_stride,
+                                              int row_lo, int* status, cudaStream_t stream) {
+  if (entries <= 0 || max_new * groups <= row_lo) return 0;
+  if (entries > 65535 || num_kv_heads > 65535) return FE_ERR_TOO_LARGE;
+  if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15) return FE_ERR_BAD_ALIGN;
+  if ((q_stride % 8) != 0) return FE_ERR_BAD_ALIGN;
+  const bool shapes = (D == 128 || D == 64) && groups >= 1 && (TC5_ROWS % groups) == 0 && page_size <= TC5_KEYS &&
+                      page_size * 32 >= TC5_KEYS && (TC5_KEYS % page_size) == 0 && scale > 0.f && keep_first >= 0;
+  if (!shapes || !ensure_encode()) return FE_ERR_BAD_SHAPE;
+  AttnParams p;
+  p.q = (const bf16*)q; p.q_stride = q_stride; p.out = (bf16*)out;
+  p.k = (const bf16*)k_cache; p.v = (const bf16*)v_cache;
+  p.block_table = block_table; p.max_pages = max_pages; p.page_size = page_size; p.num_pages = num_pages;
+  p.nkv = num_kv_heads; p.groups = groups; p.cu_tokens = cu_tokens; p.starts = starts;
+  p.window = window; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
+  p.row_lo = row_lo; p.row_hi = 0x7fffffff;
+  p.num_splits = 1; p.ws_acc = nullptr; p.ws_ml = nullptr; p.ws_count = nullptr; p.cluster_merge = 0;
+  p.keep_first = keep_first; p.gate = gate; p.gate_stride = gate_stride;
+  CUtensorMap mk, mv, mq;
+  if (!cache_map(&mk, k_cache, num_pages * num_kv_heads * page_size, page_size) ||
+      !cache_map(&mv, v_cache, num_pages * num_kv_heads * page_size, page_size) ||
+      make_query_map(&mq, q, q_stride, total_tokens, num_kv_heads * groups, groups) != 0)
+    return FE_ERR_BAD_SHAPE;
+  static bool tc5_configured = false;
+  if (!tc5_configured) {
+    const cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC5_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    tc5_configured = true;
+  }
+  const int query_blocks = (max_new * groups + TC5_BLOCK_ROWS - 1) / TC5_BLOCK_ROWS;
+  if (query_blocks > 65535) return FE_ERR_TOO_LARGE;
+  const int rc = fe_launch_dependent(attn_prefill_tc5_kernel, dim3(num_kv_heads, entries, query_blocks), dim3(TC5_THREADS),
+                                     TC5_SMEM, stream, mq, mk, mv, p);
+  return rc ? rc : fe_last_error();
+}
 
 FE_EXPORT int SYM(fe_attention_decode_noalloc_d)(const void* q, int q_stride, void* out,
                                                  const void* k_cache, const void* v_cache,

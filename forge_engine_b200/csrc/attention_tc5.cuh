@@ -245,12 +245,21 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   const Tc5Tile t1 = tc5_tile(row0 + TC5_ROWS, rows_total, start, p.groups, p.window);
   const int tile_begin = t0.tile_begin;
   const int tile_end = t1.valid ? t1.tile_end : t0.tile_end;
-  const int n_tiles = tile_end - tile_begin;
+  // Keys below keep_first stay visible behind a window: the key tiles that hold them and lie
+  // before the block's first tile are walked ahead of the others.  Step i of the walk is key
+  // tile tile_of(i).
+  const int sink_keys = p.window > 0 ? p.keep_first : 0;
+  const int sink_all = (sink_keys + TC5_KEYS - 1) / TC5_KEYS;       // key tiles that hold kept keys
+  const int sink_tiles = min(sink_all, tile_begin);
+  const int n_tiles = sink_tiles + tile_end - tile_begin;
+  auto tile_of = [&](int i) -> int { return i < sink_tiles ? i : tile_begin + i - sink_tiles; };
   const int key_end = t1.valid ? t1.key_end : t0.key_end;
   const int key_lo = p.window > 0 ? max(0, t0.pos_first - p.window + 1) : 0;
-  // does query tile x take part in key tile i (counted from tile_begin)?
+  // does query tile x take part in step i?  (Tile 1's window starts later than tile 0's; a key
+  // tile before it still counts for tile 1 when it holds kept keys.)
   auto active = [&](int x, int i) -> bool {
-    return x == 0 ? (tile_begin + i < t0.tile_end) : (t1.valid && tile_begin + i >= t1.tile_begin);
+    const int kt = tile_of(i);
+    return x == 0 ? (kt < t0.tile_end) : (t1.valid && (kt >= t1.tile_begin || kt < sink_all));
   };
 
   if (threadIdx.x == 0) {
@@ -293,7 +302,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     bool ok = true;
     for (int i = 0; i < n_tiles && ok; ++i) {
       const int ks = i % TC5_K_STAGES, vs = i % TC5_V_STAGES;
-      const int logical = (tile_begin + i) * pages_per_tile + lane;
+      const int logical = tile_of(i) * pages_per_tile + lane;
       const int key = logical * p.page_size;
       int row = rows_in_cache;            // outside the tensor: zeros
       if (lane < pages_per_tile && key < key_end) {
@@ -410,7 +419,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       ok = mbar_wait(s_full + x, count & 1, abort_flag);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int key0 = (tile_begin + i) * TC5_KEYS;
+      const int key0 = tile_of(i) * TC5_KEYS;
       unsigned raw[TC5_KEYS];
 #pragma unroll
       for (int c = 0; c < TC5_KEYS / 32; ++c) tc5_ld32_issue(s_addr + c * 32, raw + c * 32);
@@ -422,9 +431,9 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         // this row sees the keys j_lo..j_hi of the tile (none when the row is past the end)
         const int j_hi = min(pos, mine.key_end - 1) - key0;
         if (p.window > 0) {
-          const int j_lo = pos - p.window + 1 - key0;
+          const int j_lo = pos - p.window + 1 - key0, j_kept = sink_keys - key0;      // kept keys: j < j_kept
 #pragma unroll
-          for (int j = 0; j < TC5_KEYS; ++j) raw[j] = (j <= j_hi && j >= j_lo) ? raw[j] : 0xff800000u;   // -inf
+          for (int j = 0; j < TC5_KEYS; ++j) raw[j] = (j <= j_hi && (j >= j_lo || j < j_kept)) ? raw[j] : 0xff800000u;   // -inf
         } else {
 #pragma unroll
           for (int j = 0; j < TC5_KEYS; ++j) raw[j] = j <= j_hi ? raw[j] : 0xff800000u;
@@ -494,9 +503,11 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     if (ok) ok = mbar_wait(o_full, 0, abort_flag);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (ok) {
-      const float inv = l > 0.f ? 1.f / l : 0.f;
+      float inv = l > 0.f ? 1.f / l : 0.f;
       const int num_q_heads = p.nkv * p.groups;
       const int token = row / p.groups, g = row - token * p.groups;
+      if (p.gate != nullptr && row_valid)
+        inv *= 1.f / (1.f + expf(-p.gate[(size_t)(tok0 + token) * p.gate_stride + kvh * p.groups + g]));
       bf16* dst = p.out + ((size_t)(tok0 + token) * num_q_heads + kvh * p.groups + g) * D;
 #pragma unroll 1
       for (int c = 0; c < D; c += 32) {

@@ -117,6 +117,53 @@ def attention_lib(head_dim: int):
     return fn
 
 
+PREFILL_TC5_ROWS = 128     # rows of a query tile of the tcgen05 prefill attention
+PREFILL_TC5_KEYS = 128     # keys of one of its key tiles
+
+
+def prefill_tc5_takes(dtype, head_dim: int, value_dim: int, groups: int, page_size: int) -> bool:
+    """Whether the tcgen05 prefill attention runs for these sizes: bfloat16, keys and values of
+    64 or 128, heads per kv head that divide a query tile, pages of 4 to 128 keys that divide a
+    key tile."""
+    return (dtype == torch.bfloat16 and head_dim == value_dim and head_dim in (64, 128) and groups >= 1
+            and PREFILL_TC5_ROWS % groups == 0 and 4 <= page_size <= PREFILL_TC5_KEYS
+            and PREFILL_TC5_KEYS % page_size == 0 and _os.environ.get("FORGE_ENGINE_GENERAL_TC5", "1") != "0")
+
+
+def attention_prefill_tc5(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
+                          block_table: torch.Tensor, cu_tokens: torch.Tensor, starts: torch.Tensor, n_entries: int,
+                          max_new: int, num_q_heads: int, window: int | None, keep_first: int, scale: float,
+                          gate: torch.Tensor | None, row_lo: int, status: torch.Tensor) -> None:
+    """The tcgen05 prefill attention for the entries of a step with more than ``row_lo`` rows
+    (new tokens x heads per kv head): ``q`` [N, heads * D] and ``out`` [N, heads * D] bfloat16,
+    caches [pages, kv_heads, page_size, D].  ``window`` with ``keep_first``: keys below it
+    stay visible; ``gate`` (32-bit [N, >= heads]): sigmoid gates per (token, head)."""
+    _dense(q, "q"), _dense(out, "out"), _dense(k_cache, "k_cache"), _dense(v_cache, "v_cache"), _dense(block_table, "block_table")
+    num_pages, nkv, page_size, d = k_cache.shape
+    n = q.shape[0]
+    assert q.dtype == out.dtype == k_cache.dtype == v_cache.dtype == torch.bfloat16 and v_cache.shape == k_cache.shape
+    assert q.shape == out.shape == (n, num_q_heads * d) and num_q_heads % nkv == 0
+    assert gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape[0] == n)
+    handle = _attention_handle(d)
+    fn = getattr(handle, f"fe_attention_prefill_tc5_d{d}")
+    if not getattr(fn, "_declared", False):
+        p, i, f, ll = c_void_p, c_int, c_float, ctypes.c_longlong
+        fn.argtypes = [p, i, p, p, p, p, i, i, i, i, i, p, p, i, i, i, i, i, f, p, ll, i, p, p]
+        fn.restype = c_int
+        fn._declared = True
+    gate_stride = 0 if gate is None else (int(gate.stride(0)) if n > 1 else int(gate.shape[1]))
+    check(fn(ptr(q), int(q.shape[1]), ptr(out), ptr(k_cache), ptr(v_cache), ptr(block_table), block_table.shape[1],
+             page_size, num_pages, nkv, num_q_heads // nkv, ptr(cu_tokens), ptr(starts), int(n_entries), int(max_new), n,
+             int(window or 0), int(keep_first or 0), float(scale), ptr(gate), gate_stride, int(row_lo), ptr(status),
+             stream()), "attention_prefill_tc5")
+
+
+def _attention_handle(head_dim: int):
+    """The library compiled for ``head_dim`` (built and loaded on first use)."""
+    attention_lib(head_dim)
+    return _attention_handles[head_dim]
+
+
 def has_symbol(name: str) -> bool:
     return hasattr(lib(), name)
 
@@ -547,7 +594,7 @@ def general_attention_lib(key_dim: int, value_dim: int, value_in_key: bool):
         run = getattr(handle, f"fe_attention_gmma_{suffix}")
         p, i, f, ll = c_void_p, c_int, c_float, ctypes.c_longlong
         run.argtypes = [p, ll, ll, p, i, p, i, p, ll, ll, p, i, i, i, i, i, p, p, i, i, p, i, f, i, p,
-                        i, f, f, i, i, ll, i, ll, p, ll, i, p, p]
+                        i, f, f, i, i, ll, i, ll, p, ll, i, i, p, p]
         run.restype = c_int
         space = getattr(handle, f"fe_attention_gmma_workspace_{suffix}")
         space.argtypes = [i, i, i, i, i]
@@ -605,6 +652,7 @@ def attention_general(
     parts: int = 1,
     part_strides: tuple = (0, 0, 0),
     gate: torch.Tensor | None = None,
+    row_hi: int = 0,
 ) -> None:
     """Paged causal attention for any key and value size: scores, softmax and sums in 32-bit.
 
@@ -625,7 +673,9 @@ def attention_general(
     elements after the head's first, its key ``part_strides[1]`` * m elements into the cached
     row, and writes ``part_strides[2]`` * m elements after the head's first output.  ``gate``
     (32-bit [N, >= heads], a column slice is fine): row (token, head) is multiplied by
-    sigmoid(gate[token, head]).  ``out`` may be 32-bit whatever the cache holds."""
+    sigmoid(gate[token, head]).  ``out`` may be 32-bit whatever the cache holds.  ``row_hi`` > 0
+    (tensor-core kernel only): entries with more rows (new tokens x heads per kv head) are
+    skipped - another kernel serves them."""
     num_pages, nkv, page_size, k_row = k_cache.shape
     v_row = v_cache.shape[3]
     n = positions.numel()
@@ -651,13 +701,14 @@ def attention_general(
             run(ptr(q), int(q_strides[0]), int(q_strides[1]), ptr(k_cache), k_row, ptr(v_cache), v_row, ptr(out),
                 int(o_strides[0]), int(o_strides[1]), ptr(block_table), block_table.shape[1], page_size, num_pages, nkv,
                 int(num_q_heads), ptr(cu_tokens), ptr(starts), int(n_entries), int(max_new), ptr(slopes),
-                int(window or 0), float(scale), int(splits), ptr(workspace), *extras, ptr(status), stream()),
+                int(window or 0), float(scale), int(splits), ptr(workspace), *extras, int(row_hi), ptr(status), stream()),
             "attention_general (tensor cores)",
         )
         if splits > 1:
             global LAUNCHES
             LAUNCHES += 1
         return
+    assert row_hi == 0, "only the tensor-core kernel leaves entries to another kernel"
     check(
         lib().fe_attention_general(
             ptr(q), int(q_strides[0]), int(q_strides[1]), ptr(k_cache), k_row, int(k_dim), ptr(v_cache), v_row,

@@ -26,6 +26,7 @@ from .linear import Linear, fused_rows
 # the 148 SMs of a B200); a mixer asks the kernel library for the figure of its device.
 DEFAULT_DECODE_SLOTS = 296
 MAX_SPLITS = 64   # what the merge takes
+SHORT_ENTRY_ROWS = 16   # general layers: entries with more rows (new tokens x heads per kv head) may take the tcgen05 prefill kernel
 # With more tokens a block of the projection finishes so many that the separate kernel is
 # faster (measured: 2.35 -> 2.27 ms per step at 1 token, no change at 8, 6.2 -> 6.7 ms at 64).
 FUSED_PROJECTION_ROWS = 16
@@ -311,15 +312,23 @@ class GQAttention(Mixer):
         out = torch.empty((n, nq * parts * dv), dtype=k_cache.dtype if parts == 1 else torch.float32, device=x.device)
         if self.plan_key not in batch.plans:
             self.plan_step(batch.entries, k_cache.shape[2], batch.plans)
+        splits, long_entries, short_entries = batch.plans[self.plan_key]
+        gate = qkv[:, k_end + nkv * dv :] if self.head_gate else None
         with self.ctx.section("mixer.attention"):
-            native.attention_general(q, (nq * d, d), k_cache, self.d, v_cache, dv, out, (nq * parts * dv, parts * dv), table,
-                                     batch.positions, batch.token_entry, nq, self.slopes, self.spec.window,
-                                     self.spec.scale, self.ctx.status,
-                                     entries=(batch.cu_tokens, batch.starts, batch.n_entries, batch.max_new),
-                                     splits=batch.plans[self.plan_key], keep_first=self.keep_first,
-                                     softcap=self.softcap, query_temperature=self.query_temperature, parts=parts,
-                                     part_strides=(self.d, self.d, dv) if parts > 1 else (0, 0, 0),
-                                     gate=qkv[:, k_end + nkv * dv :] if self.head_gate else None)
+            if long_entries:
+                # prompt portions of a plain softmax layer with heads of 64 or 128: the tcgen05 kernel
+                native.attention_prefill_tc5(q, k_cache, v_cache, out, table, batch.cu_tokens, batch.starts, batch.n_entries,
+                                             batch.max_new, nq, self.spec.window, self.keep_first, self.spec.scale, gate,
+                                             SHORT_ENTRY_ROWS, self.ctx.status)
+            if short_entries:
+                native.attention_general(q, (nq * d, d), k_cache, self.d, v_cache, dv, out, (nq * parts * dv, parts * dv), table,
+                                         batch.positions, batch.token_entry, nq, self.slopes, self.spec.window,
+                                         self.spec.scale, self.ctx.status,
+                                         entries=(batch.cu_tokens, batch.starts, batch.n_entries, batch.max_new),
+                                         splits=splits, keep_first=self.keep_first,
+                                         softcap=self.softcap, query_temperature=self.query_temperature, parts=parts,
+                                         part_strides=(self.d, self.d, dv) if parts > 1 else (0, 0, 0),
+                                         gate=gate, row_hi=SHORT_ENTRY_ROWS if long_entries else 0)
             if parts > 1:
                 maps = out
                 out = torch.empty((n, nq * dv), dtype=k_cache.dtype, device=x.device)
@@ -376,6 +385,14 @@ class GQAttention(Mixer):
             )
         return qkv
 
+    def _prefill_tc5(self, page_size: int) -> bool:
+        """Whether prompt portions of this (general) layer run on the tcgen05 prefill kernel:
+        a plain softmax over one map per head (a window, kept first tokens and a gate per head
+        it has), keys and values of 64 or 128."""
+        return (self.parts == 1 and self.slopes is None and self.softcap is None and self.query_temperature is None
+                and self.spec.scale > 0 and native.prefill_tc5_takes(self.ctx.dtype, self.d, self.dv, self.nq // self.nkv, page_size)
+                and native.general_mma_takes(self.ctx.dtype, self.d, self.dv))
+
     def _summed_projection(self, x, rotary, k_cache) -> bool:
         """Whether the q/k/v projection adds its k-splits into a 32-bit buffer that a separate
         norm-and-rotate kernel reads: few tokens, the tcgen05 kernel takes the call, and the
@@ -404,13 +421,18 @@ class GQAttention(Mixer):
         of the decode kernel - 0: the kernel that spreads all tiles evenly) under this
         mixer's key; layers with the same geometry share it."""
         if self.general:
-            # the general kernels: how many blocks share a row tile's keys
+            # the general kernels: (how many blocks share a row tile's keys, whether entries go
+            # to the tcgen05 prefill kernel, whether entries go to the general kernel)
             if self.plan_key not in plans:
+                groups = self.nq // self.nkv
+                short = list(entries)
+                if self._prefill_tc5(page_size):
+                    short = [e for e in entries if e[2] * groups <= SHORT_ENTRY_ROWS]
                 splits = 1
-                if native.general_mma_takes(self.ctx.dtype, self.d, self.dv):
-                    splits = native.general_splits(entries, self.nq // self.nkv, self.nkv * self.parts, self.spec.window,
+                if short and native.general_mma_takes(self.ctx.dtype, self.d, self.dv):
+                    splits = native.general_splits(short, groups, self.nkv * self.parts, self.spec.window,
                                                    keep_first=self.keep_first)
-                plans[self.plan_key] = splits
+                plans[self.plan_key] = (splits, len(short) < len(entries), bool(short))
             return
         if self.ctx.dtype != torch.bfloat16 or self.plan_key in plans:
             return

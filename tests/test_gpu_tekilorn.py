@@ -442,6 +442,80 @@ def test_two_maps_per_head_and_gates(new_tokens, dtype):
         assert float((gated - ref[T - count :]).abs().max()) <= tol, splits
 
 
+@pytest.mark.parametrize("dim", (64, 128))
+@pytest.mark.parametrize("window, keep_first", ((None, 0), (40, 0), (40, 5), (200, 3), (130, 129), (7, 300)))
+def test_prompt_portions_on_the_tcgen05_kernel(window, keep_first, dim):
+    """Plain softmax layers with heads of 64 or 128 send prompt portions to the tcgen05 prefill
+    kernel: window edges, kept first tokens (fewer and more than a key tile of 128 holds, pages
+    between them and the window missing from the table), a gate per head; a whole prompt and a
+    portion that starts in the middle of a page and of a key tile, beside a second entry."""
+    from forge_engine_b200.ops import native
+
+    gen = torch.Generator().manual_seed(dim + (window or 0))
+    T, H, G, page = 420, 4, 2, 4
+    q = 0.1 * torch.randn(T, H, dim, generator=gen)
+    k = 0.1 * torch.randn(T, G, dim, generator=gen)
+    v = torch.randn(T, G, dim, generator=gen)
+    gate = 2.0 * torch.randn(T, H, generator=gen)
+    for i in range(T):
+        k[i, :, i % dim] = 4.0
+    if window is not None:
+        for i in range(T):
+            for key in (i - window + 1, i - window, keep_first - 1, keep_first):
+                q[i, :, key % dim] = 6.0
+    q, k, v = (t.to(torch.bfloat16).float() for t in (q, k, v))
+    ref = plain_scores_attention(q, k, v, 0.5, window, keep_first) * torch.sigmoid(gate.double())[:, :, None]
+    device = "cuda"
+    pages = -(-T // page)
+    order = torch.randperm(pages + 5, generator=gen)[:pages]
+    k_cache = torch.zeros(pages + 5, G, page, dim, dtype=torch.bfloat16, device=device)
+    v_cache = torch.zeros_like(k_cache)
+    for t in range(T):
+        k_cache[order[t // page], :, t % page] = k[t].to(torch.bfloat16).to(device)
+        v_cache[order[t // page], :, t % page] = v[t].to(torch.bfloat16).to(device)
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    for first in (0, 203):
+        count = T - first
+        # a second entry of three tokens (too few rows for this kernel) comes first in the batch
+        table = torch.full((2, pages), -1, dtype=torch.int32)
+        table[1] = order.to(torch.int32)
+        if window is not None and first:
+            kept = -(-min(keep_first, T) // page)
+            table[1, kept : max(kept, (first - window + 1) // page)] = -1      # given back before this step
+        table[0, 0] = int(order[0])
+        qd = torch.zeros(3 + count, H * dim, dtype=torch.bfloat16, device=device)
+        qd[3:] = q[first:].reshape(count, H * dim).to(torch.bfloat16).to(device)
+        gates = torch.zeros(3 + count, H + 3, dtype=torch.float32, device=device)[:, :H]     # rows wider than the gates
+        gates[3:] = gate[first:].to(device)
+        out = torch.zeros(3 + count, H * dim, dtype=torch.bfloat16, device=device)
+        native.attention_prefill_tc5(qd, k_cache, v_cache, out, table.to(device),
+                                     torch.tensor([0, 3, 3 + count], dtype=torch.int32, device=device),
+                                     torch.tensor([0, first], dtype=torch.int32, device=device), 2, count, H, window,
+                                     keep_first, 0.5, gates, 16, status)
+        assert int(status.item()) == 0
+        got = out[3:].float().cpu().view(count, H, dim)
+        assert float((got - ref[first:]).abs().max()) <= 3e-2, first
+        assert float(out[:3].abs().max()) == 0          # the short entry is left to the other kernel
+
+
+def test_plain_layers_with_heads_of_64_in_a_model(tmp_path):
+    """A model whose window layers have heads of 64: prompt portions run on the tcgen05 kernel,
+    short portions and single tokens on the general one, in one step where both occur."""
+    cfg = pt.config([pt.window_layer(heads=4, kv_heads=2, dim=64, vdim=64, window=70, keep_first=3, rot_dims=32),
+                     pt.window_layer(heads=2, kv_heads=2, dim=64, vdim=64, window=None, rot_dims=64, mlp=None)], width=64)
+    weights = write_model(tmp_path / "m", cfg, 23)
+    requests = {"a": tokens_of(cfg, 300, 1), "b": tokens_of(cfg, 41, 2), "c": tokens_of(cfg, 170, 3)}
+    schedule = [[("a", 200)], [("a", 1), ("b", 30), ("c", 2)], [("a", 60), ("b", 1), ("c", 100)],
+                [("a", 39), ("b", 10), ("c", 68)]]
+    for dtype in DTYPES:
+        runner = make_runner(tmp_path / "m", dtype, page_size=16, num_pages=48)
+        block = runner.model.blocks[0]
+        assert block.mixer._prefill_tc5(16) == (dtype == "bfloat16")
+        got = run_schedule(runner, requests, schedule)
+        for key, tokens in requests.items():
+            assert_close(got[key], oracle(cfg, weights, tokens), dtype, f"request {key}")
+
+
 def test_differential_combine():
     from forge_engine_b200.ops import native
 
