@@ -4,22 +4,26 @@
 // order of their experts, so that an expert's rows lie side by side and one tile of a matrix
 // product reads the expert's weights once for all of them.  Nothing is decided on the host:
 // the counts live on the device and the products are launched for the worst case
-// (ceil(slots / 64) + experts row tiles), tiles beyond the real ones returning at once.  So
+// (ceil(slots / tile) + experts row tiles), tiles beyond the real ones returning at once.  So
 // the step can be captured in a CUDA graph.
 //
-//   moe_route    one warp per token: scores from the router's 32-bit logits (sigmoid or
-//                softmax), the `top` largest (ties: the lower index), weights = the chosen
-//                scores as they are or divided by their sum; counts per expert by atomic adds,
-//                the value the add returns being the slot's rank inside its expert.
+//   moe_logits   the router's logits in plain 32-bit FMAs: a block per token and eight rows.
+//   moe_route    one warp per token: scores from the 32-bit logits (sigmoid or softmax), the
+//                `top` largest (ties: the lower index), weights = the chosen scores as they
+//                are or divided by their sum; counts per expert by atomic adds, the value the
+//                add returns being the slot's rank inside its expert.
 //   moe_plan     one block: running sum of the counts (expert e's rows are [offset[e],
-//                offset[e + 1])), the table of row tiles, every slot's row, and the counts
-//                zeroed again for the next call.
-//   moe_grouped  the products.  First: rows gathered from the tokens' activations, times the
-//                slot's weight where the weight scales the expert's input, against the expert's
+//                offset[e + 1])), the table of row tiles (of 16 to 128 rows, as the products
+//                want them), every slot's row, and the counts zeroed again for the next call.
+//   moe_gather   the rows side by side, times the slot's weight where the weight scales the
+//                expert's input: the operand of the grouped tcgen05 product (gemm_tc5.cu), which
+//                serves bfloat16 with sizes in sixteens.
+//   moe_grouped  the products for everything else (32-bit, odd sizes).  First: rows gathered
+//                from the tokens' activations, times the slot's weight, against the expert's
 //                gate and up matrices at once, the gated unit applied to the two 32-bit sums.
 //                Second: those rows against the expert's down matrix.  Plain FFMA tiles of 64 x
 //                64 (any dtype), or mma.sync tiles for bfloat16; each output element is summed
-//                over k in ascending order, so a row's result does not depend on its neighbours.
+//                over k in a fixed order, so a row's result does not depend on its neighbours.
 //   moe_combine  a token's update = the sum of its slots' rows (times the weight where it
 //                scales the output) + gate * the shared unit's output, in slot order.
 #include "common.cuh"
