@@ -516,6 +516,41 @@ def test_plain_layers_with_heads_of_64_in_a_model(tmp_path):
             assert_close(got[key], oracle(cfg, weights, tokens), dtype, f"request {key}")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_mixed_steps_replayed_from_graphs(tmp_path, dtype):
+    """Steps that bring a prompt portion beside two decoding requests, captured at first sight
+    and replayed (filler entries pad them to their bucket): the tcgen05 prefill kernel for the
+    portion, the general kernel for the single tokens, a routed layer, looped layers, kept
+    pages.  Logits at every entry's last token against the plain implementation."""
+    from forge_engine_b200.engine import StepEntry
+
+    top = 2 if dtype == "float32" else 5
+    cfg = pt.config([pt.window_layer(heads=4, kv_heads=2, dim=64, vdim=64, window=70, keep_first=3, rot_dims=32,
+                                     mlp=pt.routed(top=top, ff=32)),
+                     pt.differential_layer(mlp=None),
+                     pt.window_layer(heads=2, kv_heads=2, dim=128, vdim=128, window=150, keep_first=20, rot_dims=64)],
+                    width=64, loop=(0, 2, 2))
+    weights = write_model(tmp_path / "m", cfg, 31)
+    requests = {"a": tokens_of(cfg, 64 * 12 + 5, 1), "b": tokens_of(cfg, 22, 2), "c": tokens_of(cfg, 27, 3)}
+    schedule = [[("b", 9), ("c", 14)]] + [[("a", 64), ("b", 1), ("c", 1)] for _ in range(12)] + [[("a", 5), ("b", 1), ("c", 1)]]
+    runner = make_runner(tmp_path / "m", dtype, page_size=16, num_pages=80)
+    runner.graphs.capture_after = 1
+    refs = {key: oracle(cfg, weights, tokens).float() for key, tokens in requests.items()}
+    at = {key: 0 for key in requests}
+    for step in schedule:
+        entries = []
+        for key, count in step:
+            if at[key] == 0:
+                runner.begin(key)
+            entries.append(StepEntry(key, requests[key][at[key] : at[key] + count], [count - 1]))
+        logits = runner.step(entries).float().cpu()
+        runner.check_status()
+        for row, (key, count) in enumerate(step):
+            at[key] += count
+            assert_close(logits[row : row + 1], refs[key][at[key] - 1 : at[key]], dtype, f"{key} at {at[key] - 1}")
+    assert len(runner.graphs.captured) >= 2
+
+
 def test_differential_combine():
     from forge_engine_b200.ops import native
 
